@@ -119,15 +119,41 @@ int bt_latent_decode_finish(const float* part, const void* mixed_latent, int n_s
 int bt_latent_attention_rows(int rank, int rot, int dtype, int tensor_cores);
 int bt_lightning_scan(const void* proj, long long row_stride, int q_off, int k_off, int v_off, float* state,
                       const int* slots, const int* seq_start, const float* decay, float* out, long long out_row_stride,
-                      int n_seqs, int n_heads, int dim, int vdim, int dtype, cudaStream_t stream);
+                      int n_seqs, int n_heads, int dim, int vdim, int act, int dtype, cudaStream_t stream);
 long long bt_lightning_chunked_scratch_floats(int n_seqs, int max_new, int n_heads, int dim, int vdim);
 int bt_lightning_chunked(const void* proj, long long row_stride, int q_off, int k_off, int v_off, float* state,
                          const int* slots, const int* seq_start, const float* decay, float* out, long long out_row_stride,
-                         float* scratch, int max_new, int n_seqs, int n_heads, int dim, int vdim, int dtype,
+                         float* scratch, int max_new, int n_seqs, int n_heads, int dim, int vdim, int act, int dtype,
                          cudaStream_t stream);
 int bt_rmsnorm(const void* x, int x_dtype, long long x_row_stride, const float* weight, const void* gate, int gate_dtype,
                long long gate_row_stride, void* out, int out_dtype, long long out_row_stride, int n_rows, int width,
-               int groups, float eps, cudaStream_t stream);
+               int groups, float eps, int gate_rule, cudaStream_t stream);
+int bt_rmsnorm_add(const float* x, const float* weight, float* stream_rows, const float* next_weight, void* next_out,
+                   int next_dtype, long long n_rows, int width, float eps, cudaStream_t stream);
+int bt_polynorm(const void* x, const float* coef, void* out, long long n_rows, int width, float eps, int dtype,
+                cudaStream_t stream);
+int bt_rotary_half(const void* src, long long src_row_stride, int src_dtype, float* dst, long long dst_row_stride,
+                   const int* positions, const float* inv_freq, int n_tokens, int n_vecs, int len, int dims,
+                   int scaled_from, float scale, int tail, cudaStream_t stream);
+// A short causal convolution with its state (csrc/short_conv.cu), attention whose heads talk before the softmax
+// (csrc/talking_attention.cu) and the selective state-space scan (csrc/selective_scan.cu).
+int bt_short_conv(const void* src, long long src_row_stride, int src_dtype, const float* w, const float* bias, float* state,
+                  const int* slots, const int* seq_start, const int* token_seq, void* out, long long out_row_stride,
+                  int out_dtype, void* raw_out, long long raw_row_stride, int raw_first_group, long long n_tokens,
+                  int n_seqs, int channels, int taps, int act, int group, float eps, cudaStream_t stream);
+int bt_talking_attention(const void* q, long long q_row_stride, const void* k, const void* v, const int* kv_table,
+                         int table_stride, int table_len, int page_size, long long kv_row_stride, const void* gate,
+                         long long gate_row_stride, void* out, long long out_row_stride, const int* seq_start,
+                         const int* past_len, const float* temp, const float* slope, const float* talk, int n_seqs,
+                         int max_new, int n_heads, int n_kv_heads, int head_dim, float scale, float cap, int window,
+                         float out_scale, int dtype, cudaStream_t stream);
+int bt_selective_scan_dt(const void* low, long long low_row_stride, const float* w_dt, const float* b_dt, float* dt,
+                         long long n_tokens, int channels, int rank, int dtype, cudaStream_t stream);
+int bt_selective_scan(const void* x, long long x_row_stride, const void* z, long long z_row_stride, const float* dt,
+                      const void* low, long long low_row_stride, int b_off, int c_off, const float* a_log,
+                      const float* d_skip, float* state, const int* slots, const int* seq_start, void* out,
+                      long long out_row_stride, int n_seqs, int channels, int n_state, float out_scale, int dtype,
+                      cudaStream_t stream);
 int bt_rotary_interleaved(const void* src, long long src_row_stride, int src_vec_stride, void* dst,
                           long long dst_row_stride, int dst_vec_stride, const int* positions, const float* inv_freq,
                           int n_tokens, int n_vecs, int len, int dims, int dtype, cudaStream_t stream);

@@ -3,7 +3,8 @@
 //     S_t = decay_h * S_(t-1) + k_t v_t^T        (S: dim x vdim)
 //     o_t = S_t^T q_t
 //
-// q, k, v are act(projection) with act = x * sigmoid(x), applied here in 32-bit to the step's projections.  Columns of
+// q, k, v are act(projection), applied here in 32-bit to the step's projections: act = x * sigmoid(x) (`act` 0) or the
+// projection as it is (`act` 1: a caller that has prepared q, k, v itself, for instance rotated them).  Columns of
 // S (value channels) never mix, so a block owns a group of value channels of one (sequence, head), keeps its part of
 // the state in registers for all tokens of the step, and writes it back once.  Inside a block a value channel belongs
 // to SPLIT adjacent lanes, each with DPT of the head's `dim` key channels; their partial outputs meet by shuffles.
@@ -15,13 +16,14 @@ namespace bt {
 constexpr int LS_TOKENS = 16;  // tokens staged in shared memory at a time
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float feature(float x, int act) { return act == 0 ? silu(x) : x; }
 
 template <typename T, int DPT, int SPLIT>
 __global__ void __launch_bounds__(256)
 lightning_scan_kernel(const T* __restrict__ proj, long long row_stride, int q_off, int k_off, int v_off,
                       float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ seq_start,
                       const float* __restrict__ decay, float* __restrict__ out, long long out_row_stride, int n_heads,
-                      int dim, int vdim, int cols) {
+                      int dim, int vdim, int cols, int act) {
   extern __shared__ float sm[];
   float* q_s = sm;                          // [LS_TOKENS][dim]
   float* k_s = q_s + LS_TOKENS * dim;       // [LS_TOKENS][dim]
@@ -45,13 +47,13 @@ lightning_scan_kernel(const T* __restrict__ proj, long long row_stride, int q_of
     for (int i = threadIdx.x; i < nt * dim; i += blockDim.x) {
       const int t = i / dim, d = i - t * dim;
       const T* row = proj + (long long)(first + t0 + t) * row_stride + (long long)head * dim + d;
-      q_s[i] = silu(to_float(row[q_off]));
-      k_s[i] = silu(to_float(row[k_off]));
+      q_s[i] = feature(to_float(row[q_off]), act);
+      k_s[i] = feature(to_float(row[k_off]), act);
     }
     for (int i = threadIdx.x; i < nt * cols; i += blockDim.x) {
       const int t = i / cols, c = i - t * cols;
       v_s[i] = col0 + c < vdim
-                   ? silu(to_float(proj[(long long)(first + t0 + t) * row_stride + v_off + (long long)head * vdim + col0 + c]))
+                   ? feature(to_float(proj[(long long)(first + t0 + t) * row_stride + v_off + (long long)head * vdim + col0 + c]), act)
                    : 0.f;
     }
     __syncthreads();
@@ -82,7 +84,7 @@ lightning_scan_kernel(const T* __restrict__ proj, long long row_stride, int q_of
 template <typename T>
 static int launch_lightning(const T* proj, long long row_stride, int q_off, int k_off, int v_off, float* state,
                             const int* slots, const int* seq_start, const float* decay, float* out,
-                            long long out_row_stride, int n_seqs, int n_heads, int dim, int vdim, cudaStream_t stream) {
+                            long long out_row_stride, int n_seqs, int n_heads, int dim, int vdim, int act, cudaStream_t stream) {
   // DPT key channels per lane, SPLIT lanes per value channel: SPLIT * DPT >= dim
   int dpt, split;
   if (dim <= 32) { dpt = 8; split = 4; }
@@ -96,7 +98,7 @@ static int launch_lightning(const T* proj, long long row_stride, int q_off, int 
 #define BT_LS(DPT, SPLIT)                                                                                          \
   BT_PDL_OK("lightning_scan", launch_pdl(lightning_scan_kernel<T, DPT, SPLIT>, grid, block, smem, stream, 1, proj, \
                                          row_stride, q_off, k_off, v_off, state, slots, seq_start, decay, out,     \
-                                         out_row_stride, n_heads, dim, vdim, cols))
+                                         out_row_stride, n_heads, dim, vdim, cols, act))
   if (dpt == 8 && split == 4) BT_LS(8, 4);
   else if (dpt == 8) BT_LS(8, 8);
   else if (dpt == 16) BT_LS(16, 8);
@@ -109,7 +111,7 @@ static int launch_lightning(const T* proj, long long row_stride, int q_off, int 
 
 extern "C" int bt_lightning_scan(const void* proj, long long row_stride, int q_off, int k_off, int v_off, float* state,
                                  const int* slots, const int* seq_start, const float* decay, float* out,
-                                 long long out_row_stride, int n_seqs, int n_heads, int dim, int vdim, int dtype,
+                                 long long out_row_stride, int n_seqs, int n_heads, int dim, int vdim, int act, int dtype,
                                  cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_heads > 0 && dim > 0 && vdim > 0 && n_seqs >= 0 && n_seqs <= 65535 && n_heads <= 65535,
@@ -117,10 +119,10 @@ extern "C" int bt_lightning_scan(const void* proj, long long row_stride, int q_o
   if (n_seqs == 0) return 0;
   if (dtype == kF32)
     return launch_lightning<float>((const float*)proj, row_stride, q_off, k_off, v_off, state, slots, seq_start, decay,
-                                   out, out_row_stride, n_seqs, n_heads, dim, vdim, stream);
+                                   out, out_row_stride, n_seqs, n_heads, dim, vdim, act, stream);
   if (dtype == kBF16)
     return launch_lightning<__nv_bfloat16>((const __nv_bfloat16*)proj, row_stride, q_off, k_off, v_off, state, slots,
-                                           seq_start, decay, out, out_row_stride, n_seqs, n_heads, dim, vdim, stream);
+                                           seq_start, decay, out, out_row_stride, n_seqs, n_heads, dim, vdim, act, stream);
   return fail("lightning_scan: unknown dtype %d", dtype);
 }
 
@@ -150,7 +152,7 @@ __global__ void __launch_bounds__(256)
 lightning_chunk_kernel(const T* __restrict__ proj, long long row_stride, int q_off, int k_off, int v_off,
                        const int* __restrict__ seq_start, const float* __restrict__ decay, float* __restrict__ out,
                        long long out_row_stride, float* __restrict__ scratch, int max_chunks, int n_heads, int dim, int vdim,
-                       int cols, int col_blocks) {
+                       int cols, int col_blocks, int act) {
   extern __shared__ __align__(16) float sm[];
   float* q_t = sm;                       // [dim][LCP]   q_t[d][t]
   float* k_t = q_t + dim * LCP;          // [dim][LCP]   k_t[d][s]
@@ -173,8 +175,8 @@ lightning_chunk_kernel(const T* __restrict__ proj, long long row_stride, int q_o
     float qv = 0.f, kv = 0.f;
     if (t < len) {
       const T* row = proj + (row0 + t) * row_stride + (long long)head * dim + d;
-      qv = silu(to_float(row[q_off]));
-      kv = silu(to_float(row[k_off]));
+      qv = feature(to_float(row[q_off]), act);
+      kv = feature(to_float(row[k_off]), act);
     }
     q_t[d * LCP + t] = qv;
     k_t[d * LCP + t] = kv;
@@ -182,7 +184,7 @@ lightning_chunk_kernel(const T* __restrict__ proj, long long row_stride, int q_o
   for (int i = tid; i < LC * 64; i += 256) {
     const int t = i >> 6, c = i & 63;
     v_s[i] = (t < len && col0 + c < vdim)
-                 ? silu(to_float(proj[(row0 + t) * row_stride + v_off + (long long)head * vdim + col0 + c])) : 0.f;
+                 ? feature(to_float(proj[(row0 + t) * row_stride + v_off + (long long)head * vdim + col0 + c]), act) : 0.f;
   }
   __syncthreads();
   // scores of the chunk: tokens t = 4 ty .. and s = 4 tx ..
@@ -316,7 +318,7 @@ __global__ void __launch_bounds__(256)
 lightning_carry_kernel(const T* __restrict__ proj, long long row_stride, int q_off, const int* __restrict__ seq_start,
                        const float* __restrict__ decay, float* __restrict__ out, long long out_row_stride,
                        const float* __restrict__ scratch, int max_chunks, int n_heads, int dim, int vdim, int cols,
-                       int col_blocks) {
+                       int col_blocks, int act) {
   extern __shared__ __align__(16) float sm[];
   float* q_t = sm;                 // [dim][LCP], q_t[d][t] already scaled by decay^(t+1)
   float* s_s = q_t + dim * LCP;    // [dim][64]
@@ -332,7 +334,7 @@ lightning_carry_kernel(const T* __restrict__ proj, long long row_stride, int q_o
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
   for (int i = tid; i < LC * dim; i += 256) {
     const int t = i / dim, d = i - t * dim;
-    q_t[d * LCP + t] = t < len ? silu(to_float(proj[(row0 + t) * row_stride + q_off + (long long)head * dim + d])) *
+    q_t[d * LCP + t] = t < len ? feature(to_float(proj[(row0 + t) * row_stride + q_off + (long long)head * dim + d]), act) *
                                      powf(lam, (float)(t + 1)) : 0.f;
   }
   const float* src = scratch + ((((long long)seq * max_chunks + chunk) * n_heads + head) * dim) * vdim + col0;
@@ -371,7 +373,7 @@ template <typename T>
 static int launch_lightning_chunked(const T* proj, long long row_stride, int q_off, int k_off, int v_off, float* state,
                                     const int* slots, const int* seq_start, const float* decay, float* out,
                                     long long out_row_stride, float* scratch, int max_new, int n_seqs, int n_heads, int dim,
-                                    int vdim, cudaStream_t stream) {
+                                    int vdim, int act, cudaStream_t stream) {
   const int cols = 64;
   const int col_blocks = (vdim + cols - 1) / cols;
   const int max_chunks = (max_new + LC - 1) / LC;
@@ -389,13 +391,13 @@ static int launch_lightning_chunked(const T* proj, long long row_stride, int q_o
              "lightning_scan: cannot reserve %zu bytes of shared memory", smem_c);
   BT_PDL_OK("lightning_chunk", launch_pdl(chunk_kernel, grid, block, smem_a, stream, 1, proj, row_stride, q_off, k_off, v_off,
                                           seq_start, decay, out, out_row_stride, scratch, max_chunks, n_heads, dim, vdim,
-                                          cols, col_blocks));
+                                          cols, col_blocks, act));
   BT_PDL_OK("lightning_prefix", launch_pdl(lightning_prefix_kernel, dim3((dim * vdim + 255) / 256, n_heads, n_seqs), block, 0,
                                            stream, 1, scratch, state, slots, seq_start, decay, max_chunks, n_heads, dim,
                                            vdim));
   BT_PDL_OK("lightning_carry", launch_pdl(carry_kernel, grid, block, smem_c, stream, 1, proj, row_stride, q_off, seq_start,
                                           decay, out, out_row_stride, (const float*)scratch, max_chunks, n_heads, dim, vdim,
-                                          cols, col_blocks));
+                                          cols, col_blocks, act));
   return 0;
 }
 
@@ -411,17 +413,17 @@ extern "C" long long bt_lightning_chunked_scratch_floats(int n_seqs, int max_new
 extern "C" int bt_lightning_chunked(const void* proj, long long row_stride, int q_off, int k_off, int v_off, float* state,
                                     const int* slots, const int* seq_start, const float* decay, float* out,
                                     long long out_row_stride, float* scratch, int max_new, int n_seqs, int n_heads, int dim,
-                                    int vdim, int dtype, cudaStream_t stream) {
+                                    int vdim, int act, int dtype, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_heads > 0 && dim > 0 && dim <= 256 && vdim > 0 && n_seqs >= 0 && n_seqs <= 65535 && max_new > 0 && scratch,
            "lightning_chunked: bad sizes seqs=%d heads=%d dim=%d vdim=%d max_new=%d", n_seqs, n_heads, dim, vdim, max_new);
   if (n_seqs == 0) return 0;
   if (dtype == kF32)
     return launch_lightning_chunked<float>((const float*)proj, row_stride, q_off, k_off, v_off, state, slots, seq_start,
-                                           decay, out, out_row_stride, scratch, max_new, n_seqs, n_heads, dim, vdim, stream);
+                                           decay, out, out_row_stride, scratch, max_new, n_seqs, n_heads, dim, vdim, act, stream);
   if (dtype == kBF16)
     return launch_lightning_chunked<__nv_bfloat16>((const __nv_bfloat16*)proj, row_stride, q_off, k_off, v_off, state,
                                                    slots, seq_start, decay, out, out_row_stride, scratch, max_new, n_seqs,
-                                                   n_heads, dim, vdim, stream);
+                                                   n_heads, dim, vdim, act, stream);
   return fail("lightning_chunked: unknown dtype %d", dtype);
 }

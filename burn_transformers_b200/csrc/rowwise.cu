@@ -4,6 +4,12 @@
 
 namespace bt {
 
+// what a gate's pre-activation g multiplies a row by: sigmoid(g) (rule 0) or g * sigmoid(g) (rule 1)
+__device__ __forceinline__ float gate_value(float g, int rule) {
+  const float s = 1.f / (1.f + expf(-g));
+  return rule == 1 ? g * s : s;
+}
+
 // out[r, c] = x[r, c] / sqrt(mean_c(x[r]^2) + eps) * weight[c]  (* sigmoid(gate[r, c]) if gate)
 // With `groups` > 1 a row is `groups` runs of `width` channels, each normed by its own root mean square (heads side by
 // side); weight and gate go on over all channels of the row.
@@ -11,7 +17,7 @@ template <typename TIn, typename TGate, typename TOut>
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(const TIn* __restrict__ x, long long x_row_stride, const float* __restrict__ weight,
                const TGate* __restrict__ gate, long long gate_row_stride, TOut* __restrict__ out,
-               long long out_row_stride, int width, int groups, float eps) {
+               long long out_row_stride, int width, int groups, float eps, int gate_rule) {
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
@@ -28,7 +34,7 @@ rmsnorm_kernel(const TIn* __restrict__ x, long long x_row_stride, const float* _
   const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float v = to_float(src[c]) * inv * weight[c];
-    if (gate) v *= 1.f / (1.f + expf(-to_float(gate[(long long)r * gate_row_stride + c])));
+    if (gate) v *= gate_value(to_float(gate[(long long)r * gate_row_stride + c]), gate_rule);
     out[(long long)r * out_row_stride + c] = from_float<TOut>(v);
   }
 }
@@ -38,7 +44,7 @@ template <typename TIn, typename TGate, typename TOut, int NV>
 __global__ void __launch_bounds__(128)
 rmsnorm_warp_kernel(const TIn* __restrict__ x, long long x_row_stride, const float* __restrict__ weight,
                     const TGate* __restrict__ gate, long long gate_row_stride, TOut* __restrict__ out,
-                    long long out_row_stride, int width, int groups, long long items, float eps) {
+                    long long out_row_stride, int width, int groups, long long items, float eps, int gate_rule) {
   pdl_trigger();
   pdl_wait();
   const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -60,7 +66,7 @@ rmsnorm_warp_kernel(const TIn* __restrict__ x, long long x_row_stride, const flo
     const int c = lane + 32 * i;
     if (c < width) {
       float y = v[i] * inv * weight[first + c];
-      if (gate) y *= 1.f / (1.f + expf(-to_float(gate[r * gate_row_stride + first + c])));
+      if (gate) y *= gate_value(to_float(gate[r * gate_row_stride + first + c]), gate_rule);
       out[r * out_row_stride + first + c] = from_float<TOut>(y);
     }
   }
@@ -170,7 +176,7 @@ add_rows_kernel(float* __restrict__ x, const float* __restrict__ a, const float*
 
 template <typename TIn, typename TGate>
 static int launch_rmsnorm(const TIn* x, long long xs, const float* w, const TGate* gate, long long gs, void* out,
-                          long long os, int n_rows, int width, int groups, float eps, int out_dtype,
+                          long long os, int n_rows, int width, int groups, float eps, int out_dtype, int gate_rule,
                           cudaStream_t stream) {
   width /= groups;
   const long long items = (long long)n_rows * groups;
@@ -178,7 +184,7 @@ static int launch_rmsnorm(const TIn* x, long long xs, const float* w, const TGat
     const dim3 wgrid((unsigned)((items + 3) / 4));
 #define BT_RW(TOUT, NV)                                                                                              \
   BT_PDL_OK("rmsnorm", launch_pdl(rmsnorm_warp_kernel<TIn, TGate, TOUT, NV>, wgrid, dim3(128), 0, stream, 1, x, xs, w, \
-                                  gate, gs, (TOUT*)out, os, width, groups, items, eps))
+                                  gate, gs, (TOUT*)out, os, width, groups, items, eps, gate_rule))
     if (out_dtype == kF32) {
       if (width <= 128) BT_RW(float, 4); else BT_RW(float, 32);
     } else {
@@ -191,10 +197,10 @@ static int launch_rmsnorm(const TIn* x, long long xs, const float* w, const TGat
   const dim3 grid((unsigned)n_rows * groups);
   if (out_dtype == kF32)
     BT_PDL_OK("rmsnorm", launch_pdl(rmsnorm_kernel<TIn, TGate, float>, grid, dim3(threads), 0, stream, 1, x, xs, w,
-                                    gate, gs, (float*)out, os, width, groups, eps));
+                                    gate, gs, (float*)out, os, width, groups, eps, gate_rule));
   else
     BT_PDL_OK("rmsnorm", launch_pdl(rmsnorm_kernel<TIn, TGate, __nv_bfloat16>, grid, dim3(threads), 0, stream, 1, x,
-                                    xs, w, gate, gs, (__nv_bfloat16*)out, os, width, groups, eps));
+                                    xs, w, gate, gs, (__nv_bfloat16*)out, os, width, groups, eps, gate_rule));
   return 0;
 }
 
@@ -202,7 +208,7 @@ static int launch_rmsnorm(const TIn* x, long long xs, const float* w, const TGat
 
 extern "C" int bt_rmsnorm(const void* x, int x_dtype, long long x_row_stride, const float* weight, const void* gate,
                           int gate_dtype, long long gate_row_stride, void* out, int out_dtype, long long out_row_stride,
-                          int n_rows, int width, int groups, float eps, cudaStream_t stream) {
+                          int n_rows, int width, int groups, float eps, int gate_rule, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_rows >= 0 && width > 0 && groups > 0 && width % groups == 0 && (long long)n_rows * groups < (1ll << 31),
            "rmsnorm: bad sizes rows=%d width=%d groups=%d", n_rows, width, groups);
@@ -212,15 +218,15 @@ extern "C" int bt_rmsnorm(const void* x, int x_dtype, long long x_row_stride, co
   const bool gate_bf16 = gate != nullptr && gate_dtype == kBF16;
   if (x_dtype == kF32 && !gate_bf16)
     return launch_rmsnorm((const float*)x, x_row_stride, weight, (const float*)gate, gate_row_stride, out, out_row_stride,
-                          n_rows, width, groups, eps, out_dtype, stream);
+                          n_rows, width, groups, eps, out_dtype, gate_rule, stream);
   if (x_dtype == kF32)
     return launch_rmsnorm((const float*)x, x_row_stride, weight, (const __nv_bfloat16*)gate, gate_row_stride, out,
-                          out_row_stride, n_rows, width, groups, eps, out_dtype, stream);
+                          out_row_stride, n_rows, width, groups, eps, out_dtype, gate_rule, stream);
   if (!gate_bf16)
     return launch_rmsnorm((const __nv_bfloat16*)x, x_row_stride, weight, (const float*)gate, gate_row_stride, out,
-                          out_row_stride, n_rows, width, groups, eps, out_dtype, stream);
+                          out_row_stride, n_rows, width, groups, eps, out_dtype, gate_rule, stream);
   return launch_rmsnorm((const __nv_bfloat16*)x, x_row_stride, weight, (const __nv_bfloat16*)gate, gate_row_stride, out,
-                        out_row_stride, n_rows, width, groups, eps, out_dtype, stream);
+                        out_row_stride, n_rows, width, groups, eps, out_dtype, gate_rule, stream);
 }
 
 extern "C" int bt_rotary_interleaved(const void* src, long long src_row_stride, int src_vec_stride, void* dst,
@@ -292,5 +298,151 @@ extern "C" int bt_add_rows(float* x, const float* a, const float* b, const float
   if (n == 0) return 0;
   const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
   BT_PDL_OK("add_rows", launch_pdl(add_rows_kernel, dim3(blocks), dim3(256), 0, stream, 1, x, a, b, c, n));
+  return 0;
+}
+
+namespace bt {
+
+// stream_rows[r] += x[r] / sqrt(mean(x[r]^2) + eps) * weight: a sublayer's result, normed, joins the 32-bit stream.
+// With next_out the row that the stream then holds is normed once more (next_weight) into next_out: the norm that
+// opens the next sublayer, in the same pass over the row.
+template <typename TOut>
+__global__ void __launch_bounds__(128)
+rmsnorm_add_kernel(const float* __restrict__ x, const float* __restrict__ weight, float* __restrict__ stream_rows,
+                   const float* __restrict__ next_weight, TOut* __restrict__ next_out, int width, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const long long r = blockIdx.x;
+  const float* src = x + r * width;
+  float* dst = stream_rows + r * width;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) ss = fmaf(src[c], src[c], ss);
+  const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+  float ss2 = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = dst[c] + src[c] * inv * weight[c];
+    dst[c] = v;
+    ss2 = fmaf(v, v, ss2);
+  }
+  if (next_out == nullptr) return;
+  const float inv2 = 1.f / sqrtf(block_sum(ss2, scratch) / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x)       // (a thread reads back what it wrote itself)
+    next_out[r * width + c] = from_float<TOut>(dst[c] * inv2 * next_weight[c]);
+}
+
+// out[r] = a N(z) + b N(z^2) + c N(z^3) + e over a row z = x[r], powers element by element, N(v) = v / sqrt(mean(v^2) + eps);
+// coef = (a, b, c, e).  32-bit throughout, rounded once.
+template <typename T>
+__global__ void __launch_bounds__(256)
+polynorm_kernel(const T* __restrict__ x, const float* __restrict__ coef, T* __restrict__ out, int width, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const long long r = blockIdx.x;
+  const T* src = x + r * width;
+  float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float z = to_float(src[c]), z2 = z * z;
+    s2 += z2;
+    s4 = fmaf(z2, z2, s4);
+    s6 = fmaf(z2 * z, z2 * z, s6);
+  }
+  const float n = (float)width;
+  const float i1 = coef[0] / sqrtf(block_sum(s2, scratch) / n + eps);
+  const float i2 = coef[1] / sqrtf(block_sum(s4, scratch) / n + eps);
+  const float i3 = coef[2] / sqrtf(block_sum(s6, scratch) / n + eps);
+  const float shift = coef[3];
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float z = to_float(src[c]), z2 = z * z;
+    out[r * width + c] = from_float<T>(fmaf(z, i1, fmaf(z2, i2, fmaf(z2 * z, i3, shift))));
+  }
+}
+
+// dst[t, v, :] (32-bit) = src[t, v, :] with channel i < dims/2 paired with channel i + dims/2 and the pair turned by
+// positions[t] * inv_freq[i]; channels from `dims` on pass; vectors from `scaled_from` on are multiplied by `scale`
+// afterwards.  The `tail` channels that follow the vectors in a row are copied as they are.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rotary_half_kernel(const T* __restrict__ src, long long src_row_stride, float* __restrict__ dst, long long dst_row_stride,
+                   const int* __restrict__ positions, const float* __restrict__ inv_freq, int n_vecs, int len, int dims,
+                   int scaled_from, float scale, int tail) {
+  pdl_trigger();
+  pdl_wait();
+  const long long t = blockIdx.x;
+  const float pos = (float)positions[t];
+  const int half = dims / 2, units = len - half;      // a unit: one pair, or one channel that passes
+  const T* s_row = src + t * src_row_stride;
+  float* d_row = dst + t * dst_row_stride;
+  for (int i = threadIdx.x; i < n_vecs * units; i += blockDim.x) {
+    const int v = i / units, u = i - v * units;
+    const T* s = s_row + (long long)v * len;
+    float* d = d_row + (long long)v * len;
+    const float f = v >= scaled_from ? scale : 1.f;
+    if (u < half) {
+      float sn, cs;
+      sincosf(pos * inv_freq[u], &sn, &cs);
+      const float a = to_float(s[u]), b = to_float(s[u + half]);
+      d[u] = (a * cs - b * sn) * f;
+      d[u + half] = (b * cs + a * sn) * f;
+    } else {
+      d[half + u] = to_float(s[half + u]) * f;
+    }
+  }
+  const int base = n_vecs * len;
+  for (int i = threadIdx.x; i < tail; i += blockDim.x) d_row[base + i] = to_float(s_row[base + i]);
+}
+
+}  // namespace bt
+
+extern "C" int bt_rmsnorm_add(const float* x, const float* weight, float* stream_rows, const float* next_weight,
+                              void* next_out, int next_dtype, long long n_rows, int width, float eps, cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(n_rows >= 0 && n_rows < (1ll << 31) && width > 0, "rmsnorm_add: bad sizes rows=%lld width=%d", n_rows, width);
+  BT_CHECK(next_out == nullptr || (next_weight != nullptr && (next_dtype == kF32 || next_dtype == kBF16)),
+           "rmsnorm_add: the second norm needs a weight and a known dtype");
+  if (n_rows == 0) return 0;
+  if (next_out != nullptr && next_dtype == kBF16)
+    BT_PDL_OK("rmsnorm_add", launch_pdl(rmsnorm_add_kernel<__nv_bfloat16>, dim3((unsigned)n_rows), dim3(128), 0, stream, 1, x,
+                                        weight, stream_rows, next_weight, (__nv_bfloat16*)next_out, width, eps));
+  else
+    BT_PDL_OK("rmsnorm_add", launch_pdl(rmsnorm_add_kernel<float>, dim3((unsigned)n_rows), dim3(128), 0, stream, 1, x, weight,
+                                        stream_rows, next_weight, (float*)next_out, width, eps));
+  return 0;
+}
+
+extern "C" int bt_polynorm(const void* x, const float* coef, void* out, long long n_rows, int width, float eps, int dtype,
+                           cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(n_rows >= 0 && n_rows < (1ll << 31) && width > 0, "polynorm: bad sizes rows=%lld width=%d", n_rows, width);
+  if (n_rows == 0) return 0;
+  if (dtype == kF32)
+    BT_PDL_OK("polynorm", launch_pdl(polynorm_kernel<float>, dim3((unsigned)n_rows), dim3(256), 0, stream, 1, (const float*)x,
+                                     coef, (float*)out, width, eps));
+  else if (dtype == kBF16)
+    BT_PDL_OK("polynorm", launch_pdl(polynorm_kernel<__nv_bfloat16>, dim3((unsigned)n_rows), dim3(256), 0, stream, 1,
+                                     (const __nv_bfloat16*)x, coef, (__nv_bfloat16*)out, width, eps));
+  else
+    return fail("polynorm: unknown dtype %d", dtype);
+  return 0;
+}
+
+extern "C" int bt_rotary_half(const void* src, long long src_row_stride, int src_dtype, float* dst, long long dst_row_stride,
+                              const int* positions, const float* inv_freq, int n_tokens, int n_vecs, int len, int dims,
+                              int scaled_from, float scale, int tail, cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(n_vecs > 0 && len > 0 && dims >= 0 && dims <= len && dims % 2 == 0 && tail >= 0,
+           "rotary_half: bad sizes vectors=%d len=%d dims=%d", n_vecs, len, dims);
+  if (n_tokens == 0) return 0;
+  if (src_dtype == kF32)
+    BT_PDL_OK("rotary_half", launch_pdl(rotary_half_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, 1, (const float*)src,
+                                        src_row_stride, dst, dst_row_stride, positions, inv_freq, n_vecs, len, dims,
+                                        scaled_from, scale, tail));
+  else if (src_dtype == kBF16)
+    BT_PDL_OK("rotary_half", launch_pdl(rotary_half_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), 0, stream, 1,
+                                        (const __nv_bfloat16*)src, src_row_stride, dst, dst_row_stride, positions, inv_freq,
+                                        n_vecs, len, dims, scaled_from, scale, tail));
+  else
+    return fail("rotary_half: unknown dtype %d", src_dtype);
   return 0;
 }

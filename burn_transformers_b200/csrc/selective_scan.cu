@@ -1,0 +1,205 @@
+// A selective state-space scan: per channel c and state index n a 32-bit state that every token decays and feeds,
+//
+//     dt[t, c] = softplus(sum_r W_dt[c, r] * low[t, r] + b_dt[c])                       (selective_scan_dt)
+//     S[c, n] <- exp(dt[t, c] * A[c, n]) * S[c, n] + dt[t, c] * x[t, c] * B[t, n]       A = -exp(A_log)
+//     y[t, c]  = (sum_n S[c, n] * C[t, n] + D[c] * x[t, c]) * z[t, c] * sigmoid(z[t, c]) * out_scale
+//
+// B and C are channels of the step's rows `low` (one vector per token, shared by all channels); x and z are channels
+// of other rows.  Step sizes, decays, the state and all sums are 32-bit.  A channel belongs to LANES adjacent lanes,
+// each with NS of the `n_state` indices in registers for all tokens of the step; their partial sums meet by shuffles.
+// The tokens of a run are staged in shared memory TT at a time.  state: [slots][channels][n_state].
+#include "common.cuh"
+
+namespace bt {
+
+constexpr int SS_TT = 16;        // tokens staged at a time
+constexpr int SS_THREADS = 128;
+
+__device__ __forceinline__ float ss_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// dt[t, c], a block: 256 channels x SS_TT tokens; W_dt's rows of these channels lie transposed in shared memory
+template <typename T>
+__global__ void __launch_bounds__(256)
+selective_scan_dt_kernel(const T* __restrict__ low, long long low_row_stride, const float* __restrict__ w_dt,
+                         const float* __restrict__ b_dt, float* __restrict__ dt, long long n_tokens, int channels,
+                         int rank) {
+  extern __shared__ float sm[];
+  float* w_s = sm;                    // [rank][256]
+  float* low_s = w_s + rank * 256;    // [SS_TT][rank]
+  pdl_trigger();
+  const int c0 = blockIdx.x * 256, c = c0 + threadIdx.x;
+  for (int i = threadIdx.x; i < rank * 256; i += 256) {
+    const int cl = i / rank, r = i - cl * rank;
+    w_s[r * 256 + cl] = c0 + cl < channels ? w_dt[(long long)(c0 + cl) * rank + r] : 0.f;
+  }
+  const float bias = c < channels ? b_dt[c] : 0.f;
+  pdl_wait();
+  for (long long t0 = (long long)blockIdx.y * SS_TT; t0 < n_tokens; t0 += (long long)gridDim.y * SS_TT) {
+    const int nt = (int)min((long long)SS_TT, n_tokens - t0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * rank; i += 256) {
+      const int t = i / rank, r = i - t * rank;
+      low_s[i] = to_float(low[(t0 + t) * low_row_stride + r]);
+    }
+    __syncthreads();
+    if (c < channels) {
+      for (int t = 0; t < nt; ++t) {
+        float acc = bias;
+        for (int r = 0; r < rank; ++r) acc = fmaf(w_s[r * 256 + threadIdx.x], low_s[t * rank + r], acc);
+        dt[(t0 + t) * channels + c] = ss_softplus(acc);
+      }
+    }
+  }
+}
+
+template <typename T, int NS, int LANES>
+__global__ void __launch_bounds__(SS_THREADS)
+selective_scan_kernel(const T* __restrict__ x, long long x_row_stride, const T* __restrict__ z, long long z_row_stride,
+                      const float* __restrict__ dt, const T* __restrict__ low, long long low_row_stride, int b_off,
+                      int c_off, const float* __restrict__ a_log, const float* __restrict__ d_skip,
+                      float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ seq_start,
+                      T* __restrict__ out, long long out_row_stride, int channels, int n_state, float out_scale) {
+  constexpr int CPB = SS_THREADS / LANES;      // channels per block
+  extern __shared__ float sm[];
+  float* bc_s = sm;                            // [SS_TT][2 * n_state]
+  float* dt_s = bc_s + SS_TT * 2 * n_state;    // [SS_TT][CPB]
+  float* x_s = dt_s + SS_TT * CPB;
+  float* z_s = x_s + SS_TT * CPB;
+  pdl_trigger();
+  const int seq = blockIdx.y, c_local = threadIdx.x / LANES, part = threadIdx.x % LANES;
+  const int c = blockIdx.x * CPB + c_local;
+  const bool owns = c < channels;
+  const int n0 = part * NS;
+  float a[NS], s[NS];
+#pragma unroll
+  for (int i = 0; i < NS; ++i) a[i] = owns && n0 + i < n_state ? -expf(a_log[(long long)c * n_state + n0 + i]) : 0.f;
+  const float skip = owns ? d_skip[c] : 0.f;
+  pdl_wait();
+  const int first = seq_start[seq], n_new = seq_start[seq + 1] - first;
+  float* s_base = state + ((long long)slots[seq] * channels + (owns ? c : 0)) * n_state;
+#pragma unroll
+  for (int i = 0; i < NS; ++i) s[i] = owns && n0 + i < n_state ? s_base[n0 + i] : 0.f;
+  for (int t0 = 0; t0 < n_new; t0 += SS_TT) {
+    const int nt = min(SS_TT, n_new - t0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * 2 * n_state; i += SS_THREADS) {
+      const int t = i / (2 * n_state), n = i - t * 2 * n_state;
+      const T* row = low + (long long)(first + t0 + t) * low_row_stride;
+      bc_s[i] = to_float(n < n_state ? row[b_off + n] : row[c_off + n - n_state]);
+    }
+    for (int i = threadIdx.x; i < nt * CPB; i += SS_THREADS) {
+      const int t = i / CPB, cl = i - t * CPB, cc = blockIdx.x * CPB + cl;
+      const long long r = first + t0 + t;
+      const bool in = cc < channels;
+      dt_s[i] = in ? dt[r * channels + cc] : 0.f;
+      x_s[i] = in ? to_float(x[r * x_row_stride + cc]) : 0.f;
+      z_s[i] = in ? to_float(z[r * z_row_stride + cc]) : 0.f;
+    }
+    __syncthreads();
+    for (int t = 0; t < nt; ++t) {
+      const float d = dt_s[t * CPB + c_local], xv = x_s[t * CPB + c_local];
+      const float dx = d * xv;
+      const float* bt_ = bc_s + t * 2 * n_state + n0;
+      const float* ct_ = bt_ + n_state;
+      float y = 0.f;
+#pragma unroll
+      for (int i = 0; i < NS; ++i) {
+        if (n0 + i < n_state) {
+          s[i] = fmaf(expf(d * a[i]), s[i], dx * bt_[i]);
+          y = fmaf(s[i], ct_[i], y);
+        }
+      }
+#pragma unroll
+      for (int o = 1; o < LANES; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+      if (owns && part == 0) {
+        const float zv = z_s[t * CPB + c_local];
+        const float r = (y + skip * xv) * (zv / (1.f + expf(-zv))) * out_scale;
+        out[(long long)(first + t0 + t) * out_row_stride + c] = from_float<T>(r);
+      }
+    }
+  }
+  if (owns) {
+#pragma unroll
+    for (int i = 0; i < NS; ++i)
+      if (n0 + i < n_state) s_base[n0 + i] = s[i];
+  }
+}
+
+template <typename T>
+static int launch_selective_scan(const T* x, long long xs, const T* z, long long zs, const float* dt, const T* low,
+                                 long long ls, int b_off, int c_off, const float* a_log, const float* d_skip, float* state,
+                                 const int* slots, const int* seq_start, T* out, long long os, int n_seqs, int channels,
+                                 int n_state, float out_scale, cudaStream_t stream) {
+  int ns, lanes;
+  if (n_state <= 16) { ns = 4; lanes = 4; }
+  else if (n_state <= 32) { ns = 8; lanes = 4; }
+  else if (n_state <= 64) { ns = 16; lanes = 4; }
+  else if (n_state <= 128) { ns = 16; lanes = 8; }
+  else if (n_state <= 256) { ns = 16; lanes = 16; }
+  else { ns = 16; lanes = 32; }
+  BT_CHECK(n_state <= 512, "selective_scan: %d state indices a channel; the kernel takes up to 512", n_state);
+  const int cpb = SS_THREADS / lanes;
+  const dim3 grid((channels + cpb - 1) / cpb, n_seqs);
+  const size_t smem = sizeof(float) * ((size_t)SS_TT * 2 * n_state + 3 * (size_t)SS_TT * cpb);
+#define BT_SS(NS, LANES)                                                                                              \
+  BT_PDL_OK("selective_scan", launch_pdl(selective_scan_kernel<T, NS, LANES>, grid, dim3(SS_THREADS), smem, stream, 1, x, \
+                                         xs, z, zs, dt, low, ls, b_off, c_off, a_log, d_skip, state, slots, seq_start,  \
+                                         out, os, channels, n_state, out_scale))
+  if (ns == 4) BT_SS(4, 4);
+  else if (ns == 8) BT_SS(8, 4);
+  else if (lanes == 4) BT_SS(16, 4);
+  else if (lanes == 8) BT_SS(16, 8);
+  else if (lanes == 16) BT_SS(16, 16);
+  else BT_SS(16, 32);
+#undef BT_SS
+  return 0;
+}
+
+}  // namespace bt
+
+// dt [tokens, channels] 32-bit from the first `rank` channels of the rows of low
+extern "C" int bt_selective_scan_dt(const void* low, long long low_row_stride, const float* w_dt, const float* b_dt,
+                                    float* dt, long long n_tokens, int channels, int rank, int dtype, cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(channels > 0 && rank > 0 && rank <= 160 && n_tokens >= 0,
+           "selective_scan_dt: bad sizes channels=%d rank=%d (at most 160)", channels, rank);
+  if (n_tokens == 0) return 0;
+  const size_t smem = sizeof(float) * ((size_t)rank * 256 + (size_t)SS_TT * rank);
+  const long long tiles = (n_tokens + SS_TT - 1) / SS_TT;
+  const dim3 grid((channels + 255) / 256, (unsigned)(tiles < 4096 ? tiles : 4096));
+#define BT_SSD(T)                                                                                                     \
+  do {                                                                                                                \
+    auto kern = selective_scan_dt_kernel<T>;                                                                          \
+    if (smem > 48 * 1024)                                                                                             \
+      BT_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess,     \
+               "selective_scan_dt: cannot reserve %zu bytes of shared memory", smem);                                 \
+    BT_PDL_OK("selective_scan_dt", launch_pdl(kern, grid, dim3(256), smem, stream, 1, (const T*)low, low_row_stride, w_dt, \
+                                              b_dt, dt, n_tokens, channels, rank));                                    \
+  } while (0)
+  if (dtype == kF32) BT_SSD(float);
+  else if (dtype == kBF16) BT_SSD(__nv_bfloat16);
+  else return fail("selective_scan_dt: unknown dtype %d", dtype);
+#undef BT_SSD
+  return 0;
+}
+
+// x, z, out: first channel of [tokens, channels] views; low: the rows that hold B at b_off and C at c_off
+extern "C" int bt_selective_scan(const void* x, long long x_row_stride, const void* z, long long z_row_stride,
+                                 const float* dt, const void* low, long long low_row_stride, int b_off, int c_off,
+                                 const float* a_log, const float* d_skip, float* state, const int* slots,
+                                 const int* seq_start, void* out, long long out_row_stride, int n_seqs, int channels,
+                                 int n_state, float out_scale, int dtype, cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(channels > 0 && n_state > 0 && n_seqs >= 0 && n_seqs <= 65535, "selective_scan: bad sizes seqs=%d channels=%d "
+           "state=%d", n_seqs, channels, n_state);
+  if (n_seqs == 0) return 0;
+  if (dtype == kF32)
+    return launch_selective_scan((const float*)x, x_row_stride, (const float*)z, z_row_stride, dt, (const float*)low,
+                                 low_row_stride, b_off, c_off, a_log, d_skip, state, slots, seq_start, (float*)out,
+                                 out_row_stride, n_seqs, channels, n_state, out_scale, stream);
+  if (dtype == kBF16)
+    return launch_selective_scan((const __nv_bfloat16*)x, x_row_stride, (const __nv_bfloat16*)z, z_row_stride, dt,
+                                 (const __nv_bfloat16*)low, low_row_stride, b_off, c_off, a_log, d_skip, state, slots,
+                                 seq_start, (__nv_bfloat16*)out, out_row_stride, n_seqs, channels, n_state, out_scale, stream);
+  return fail("selective_scan: unknown dtype %d", dtype);
+}

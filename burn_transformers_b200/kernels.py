@@ -760,9 +760,9 @@ def lightning_chunked_scratch_floats(n_seqs, max_new, n_heads, dim, vdim) -> int
 
 
 def lightning_scan(proj, q_off, k_off, v_off, state, slots, seq_start, decay, out, *, n_seqs, n_heads, dim, vdim,
-                   max_new=None, scratch=None):
+                   max_new=None, scratch=None, activation="swish"):
     """Runs S <- decay_h S + k v^T, o = S^T q over the step's tokens of every sequence, with q, k, v = x * sigmoid(x) of
-    the channels at `q_off`, `k_off`, `v_off` of the rows of `proj`.  state: [slots, heads, dim, vdim] 32-bit, read and
+    the channels at `q_off`, `k_off`, `v_off` of the rows of `proj` (`activation` None: the channels as they are).  state: [slots, heads, dim, vdim] 32-bit, read and
     written at the rows `slots[seq]`; out: [tokens, heads * vdim] 32-bit.
 
     With `max_new` (no sequence brings more tokens) above LIGHTNING_CHUNK and `scratch` (32-bit,
@@ -773,6 +773,9 @@ def lightning_scan(proj, q_off, k_off, v_off, state, slots, seq_start, decay, ou
     _need(out, "out", torch.float32, (None, n_heads * vdim))
     if max(q_off, k_off) + n_heads * dim > proj.shape[1] or v_off + n_heads * vdim > proj.shape[1]:
         raise ShapeError("lightning_scan: the channel offsets leave the rows of proj")
+    if activation not in ("swish", None):
+        raise ShapeError(f"lightning_scan: unknown activation {activation!r}")
+    act = c_int(0 if activation == "swish" else 1)
     n_rows = out.shape[0]
     _work(4.0 * n_rows * n_heads * dim * vdim, n_rows * n_heads * ((2 * dim + vdim) * proj.element_size() + 4 * vdim)
           + 8.0 * n_seqs * n_heads * dim * vdim)
@@ -783,19 +786,25 @@ def lightning_scan(proj, q_off, k_off, v_off, state, slots, seq_start, decay, ou
         _check(library().bt_lightning_chunked(_ptr(proj), c_longlong(proj.shape[1]), c_int(q_off), c_int(k_off),
                                               c_int(v_off), _ptr(state), _ptr(slots), _ptr(seq_start), _ptr(decay),
                                               _ptr(out), c_longlong(out.shape[1]), _ptr(scratch), c_int(max_new),
-                                              c_int(n_seqs), c_int(n_heads), c_int(dim), c_int(vdim),
+                                              c_int(n_seqs), c_int(n_heads), c_int(dim), c_int(vdim), act,
                                               c_int(_code(proj.dtype)), _stream()))
         return
     _check(library().bt_lightning_scan(_ptr(proj), c_longlong(proj.shape[1]), c_int(q_off), c_int(k_off), c_int(v_off),
                                        _ptr(state), _ptr(slots), _ptr(seq_start), _ptr(decay), _ptr(out),
                                        c_longlong(out.shape[1]), c_int(n_seqs), c_int(n_heads), c_int(dim), c_int(vdim),
-                                       c_int(_code(proj.dtype)), _stream()))
+                                       act, c_int(_code(proj.dtype)), _stream()))
 
 
-def rmsnorm(x, weight, out, eps: float, *, n_rows, gate=None, groups: int = 1):
+GATE_RULES = {"sigmoid": 0, "swish": 1}
+
+
+def rmsnorm(x, weight, out, eps: float, *, n_rows, gate=None, groups: int = 1, gate_rule: str = "sigmoid"):
     """out[r] = x[r] / sqrt(mean(x[r]^2) + eps) * weight  (* sigmoid(gate[r]) if `gate`), in 32-bit.  x, gate and out are
     2-D views with contiguous channels (rows may lie further apart); 32-bit or bfloat16 each.  With `groups` > 1 a row
-    is that many equal runs of channels (heads side by side), each divided by its own root mean square."""
+    is that many equal runs of channels (heads side by side), each divided by its own root mean square.  `gate_rule`
+    "swish" multiplies by gate * sigmoid(gate) instead."""
+    if gate_rule not in GATE_RULES:
+        raise ShapeError(f"rmsnorm: unknown gate rule {gate_rule!r}")
     width = weight.shape[0]
     if groups <= 0 or width % groups:
         raise ShapeError(f"rmsnorm: {width} channels are no {groups} equal groups")
@@ -808,7 +817,7 @@ def rmsnorm(x, weight, out, eps: float, *, n_rows, gate=None, groups: int = 1):
                                 c_int(_code(gate.dtype)) if gate is not None else c_int(0),
                                 c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out), c_int(_code(out.dtype)),
                                 c_longlong(out.stride(0)), c_int(n_rows), c_int(width), c_int(groups), c_float(eps),
-                                _stream()))
+                                c_int(GATE_RULES[gate_rule]), _stream()))
 
 
 def rotary_interleaved(src, dst, positions, inv_freq, *, n_tokens, dims):
@@ -1110,3 +1119,183 @@ def latent_decode_finish(uv_heads, out, *, n_tokens, n_splits, scratch=None, mix
                                              _ptr(gate), c_longlong(g_rs), _ptr(out), c_longlong(out.shape[1]),
                                              c_int(n_tokens), c_int(n_heads), c_int(rank), c_int(vdim),
                                              c_int(_code(uv_heads.dtype)), _stream()))
+
+
+# ---- a sublayer's normed result into the stream; the polynomial activation; the half-split rotation -----------------
+
+def rmsnorm_add(x, weight, stream_rows, eps: float, *, n_rows, next_weight=None, next_out=None):
+    """stream_rows[r] += x[r] / sqrt(mean(x[r]^2) + eps) * weight for contiguous 32-bit [rows, width] tensors.  With
+    `next_weight` and `next_out` ([rows, width], 32-bit or bfloat16) the updated row is normed again into next_out."""
+    width = weight.shape[0]
+    _need(x, "x", torch.float32, (None, width))
+    _need(stream_rows, "stream_rows", torch.float32, (None, width))
+    _need(weight, "weight", torch.float32, (width,))
+    if min(x.shape[0], stream_rows.shape[0]) < n_rows:
+        raise ShapeError(f"rmsnorm_add: {n_rows} rows asked of shorter tensors")
+    if (next_weight is None) != (next_out is None):
+        raise ShapeError("rmsnorm_add: the second norm needs both a weight and a place for its rows")
+    if next_out is not None:
+        _need(next_weight, "next_weight", torch.float32, (width,))
+        _need(next_out, "next_out", (torch.float32, torch.bfloat16), (None, width))
+        if next_out.shape[0] < n_rows:
+            raise ShapeError(f"rmsnorm_add: {n_rows} rows asked of next_out[{next_out.shape[0]}]")
+    _work(0.0, n_rows * width * (12.0 + (next_out.element_size() if next_out is not None else 0)))
+    _check(library().bt_rmsnorm_add(_ptr(x), _ptr(weight), _ptr(stream_rows), _ptr(next_weight), _ptr(next_out),
+                                    c_int(_code(next_out.dtype)) if next_out is not None else c_int(0),
+                                    c_longlong(n_rows), c_int(width), c_float(eps), _stream()))
+
+
+def polynorm(x, coef, out, eps: float, *, n_rows):
+    """out[r] = a N(z) + b N(z^2) + c N(z^3) + e for every row z of x, with the powers taken element by element,
+    N(v) = v / sqrt(mean(v^2) + eps) over the row and coef = (a, b, c, e) 32-bit on the device; 32-bit arithmetic."""
+    _need(x, "x", (torch.float32, torch.bfloat16))
+    _need(out, "out", x.dtype, (None, x.shape[1]))
+    _need(coef, "coef", torch.float32, (4,))
+    if min(x.shape[0], out.shape[0]) < n_rows:
+        raise ShapeError(f"polynorm: {n_rows} rows asked of shorter tensors")
+    _work(0.0, 2.0 * n_rows * x.shape[1] * x.element_size())
+    _check(library().bt_polynorm(_ptr(x), _ptr(coef), _ptr(out), c_longlong(n_rows), c_int(x.shape[1]), c_float(eps),
+                                 c_int(_code(x.dtype)), _stream()))
+
+
+def rotary_half(src, dst, positions, inv_freq, *, n_tokens, n_vecs, length, dims, scaled_from=None, scale=1.0, tail=0):
+    """dst (32-bit) = the first n_vecs * length channels of src's rows as vectors of `length` channels, channel i <
+    dims / 2 of each paired with channel i + dims / 2 and the pair turned by positions[t] * inv_freq[i] (32-bit angles);
+    vectors from `scaled_from` on are then multiplied by `scale`; the `tail` channels after the vectors are copied."""
+    need = n_vecs * length + tail
+    for name, t in (("src", src), ("dst", dst)):
+        if t.dim() != 2 or t.shape[1] < need or t.stride(1) != 1 or not t.is_cuda or t.shape[0] < n_tokens:
+            raise ShapeError(f"rotary_half: {name} must be a device view [>= {n_tokens}, >= {need}] with contiguous channels")
+    if dst.dtype != torch.float32 or src.dtype not in DTYPE_CODE:
+        raise ShapeError("rotary_half: dst is 32-bit, src 32-bit or bfloat16")
+    _need(inv_freq, "inv_freq", torch.float32)
+    if inv_freq.numel() < dims // 2:
+        raise ShapeError(f"rotary_half: {inv_freq.numel()} frequencies for {dims} rotated channels")
+    _check(library().bt_rotary_half(_ptr(src), c_longlong(src.stride(0)), c_int(_code(src.dtype)), _ptr(dst),
+                                    c_longlong(dst.stride(0)), _ptr(positions), _ptr(inv_freq), c_int(n_tokens),
+                                    c_int(n_vecs), c_int(length), c_int(dims),
+                                    c_int(n_vecs if scaled_from is None else scaled_from), c_float(scale), c_int(tail),
+                                    _stream()))
+
+
+# ---- short convolution, talking attention, selective scan -------------------------------------------------------------
+
+def _channels_view(t, name, rows, width):
+    if t.dim() != 2 or t.shape[1] != width or t.stride(1) != 1 or not t.is_cuda or t.shape[0] < rows:
+        raise ShapeError(f"{name} must be a device view [>= {rows}, {width}] with contiguous channels, found "
+                         f"{list(t.shape)} strides {list(t.stride())}")
+
+
+def short_conv(src, weight, bias, state, slots, seq_start, token_seq, out, *, n_tokens, n_seqs, activation=None,
+               norm_group=0, eps=0.0, raw_out=None, raw_first_group=0):
+    """y[t, c] = act(bias[c] + sum_j weight[c, j] * u[t - taps + 1 + j, c]) over the step's rows `src` [tokens, channels],
+    causal within each sequence; the inputs before the step come from `state` [slots, taps - 1, channels] (32-bit, zeros
+    for a new sequence), which afterwards holds the sequences' newest inputs.  `activation` "swish": x * sigmoid(x).
+    With `norm_group` every run of that many channels of y is divided by its root mean square (eps inside the root) and,
+    with `raw_out`, the runs from `raw_first_group` on are also written undivided there."""
+    channels, taps = weight.shape
+    _need(weight, "weight", torch.float32)
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (channels,))
+    _need(state, "state", torch.float32, (None, max(taps - 1, 0), channels))
+    _channels_view(src, "short_conv: src", n_tokens, channels)
+    _channels_view(out, "short_conv: out", n_tokens, channels)
+    if src.dtype not in DTYPE_CODE or out.dtype not in DTYPE_CODE:
+        raise ShapeError("short_conv: rows are 32-bit or bfloat16")
+    if activation not in (None, "swish"):
+        raise ShapeError(f"short_conv: unknown activation {activation!r}")
+    raw_stride = 0
+    if raw_out is not None:
+        if not norm_group or raw_out.dtype != out.dtype:
+            raise ShapeError("short_conv: undivided rows come with a norm only, in the type of out")
+        _channels_view(raw_out, "short_conv: raw_out", n_tokens, channels - raw_first_group * norm_group)
+        raw_stride = raw_out.stride(0)
+    _work(2.0 * n_tokens * channels * taps, n_tokens * channels * (src.element_size() + out.element_size()))
+    _check(library().bt_short_conv(_ptr(src), c_longlong(src.stride(0)), c_int(_code(src.dtype)), _ptr(weight), _ptr(bias),
+                                   _ptr(state), _ptr(slots), _ptr(seq_start), _ptr(token_seq), _ptr(out),
+                                   c_longlong(out.stride(0)), c_int(_code(out.dtype)), _ptr(raw_out), c_longlong(raw_stride),
+                                   c_int(raw_first_group), c_longlong(n_tokens), c_int(n_seqs), c_int(channels), c_int(taps),
+                                   c_int(1 if activation == "swish" else 0), c_int(norm_group), c_float(eps), _stream()))
+
+
+def talking_attention(q, out, seq_start, past_len, *, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale, window=0,
+                      cap=0.0, temp=None, slope=None, talk=None, gate=None, out_scale=1.0, k=None, v=None, k_pool=None,
+                      v_pool=None, table=None, table_len=0):
+    """Causal (windowed) attention over all heads of a token at once (csrc/talking_attention.cu):
+    raw_g = cap tanh((q_g . k_g) scale temp[g] / cap) - slope[g] (i - j), s_h = sum_g talk[h, g] raw_g, softmax over the
+    visible keys, the value mix, times sigmoid(gate) and out_scale.  q, gate, out: views [tokens, heads * head_dim];
+    keys and values either views [tokens, kv_heads * head_dim] of the step's own rows (`k`, `v`: sequences that start in
+    this step) or the pages of the cache."""
+    width = n_heads * head_dim
+    for name, t in (("q", q), ("out", out)) + ((("gate", gate),) if gate is not None else ()):
+        _channels_view(t, "talking_attention: " + name, 0, width)
+        if t.dtype != q.dtype:
+            raise ShapeError("talking_attention: q, gate and out have one type")
+    if q.dtype not in DTYPE_CODE:
+        raise ShapeError("talking_attention: rows are 32-bit or bfloat16")
+    for name, t, shape in (("temp", temp, (n_heads,)), ("slope", slope, (n_heads,)), ("talk", talk, (n_heads, n_heads))):
+        if t is not None:
+            _need(t, name, torch.float32, shape)
+    if table is None:
+        for name, t in (("k", k), ("v", v)):
+            _channels_view(t, "talking_attention: " + name, 0, n_kv_heads * head_dim)
+            if t.dtype != q.dtype or t.stride(0) != k.stride(0):
+                raise ShapeError("talking_attention: k and v are rows of one tensor of q's type")
+        k_ptr, v_ptr, t_ptr, t_stride, kv_stride = _ptr(k), _ptr(v), c_void_p(0), 0, k.stride(0)
+    else:
+        _need(k_pool, "k_pool", q.dtype)
+        _need(v_pool, "v_pool", q.dtype)
+        _need(table, "table", torch.int32)
+        k_ptr, v_ptr, t_ptr, t_stride, kv_stride = _ptr(k_pool), _ptr(v_pool), _ptr(table), table.shape[1], 0
+    if _PROFILE is not None:
+        seen = float(min(window or 1 << 30, _PROFILE.context_hint or max_new))
+        rows = float(out.shape[0] if max_new > 1 else n_seqs)
+        _work(4.0 * rows * n_heads * seen * head_dim, rows * (2 * width + 2 * n_kv_heads * head_dim) * q.element_size())
+    _check(library().bt_talking_attention(
+        _ptr(q), c_longlong(q.stride(0)), k_ptr, v_ptr, t_ptr, c_int(t_stride), c_int(table_len), c_int(PAGE_SIZE),
+        c_longlong(kv_stride), _ptr(gate), c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out),
+        c_longlong(out.stride(0)), _ptr(seq_start), _ptr(past_len), _ptr(temp), _ptr(slope), _ptr(talk), c_int(n_seqs),
+        c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_float(cap), c_int(window),
+        c_float(out_scale), c_int(_code(q.dtype)), _stream()))
+
+
+def selective_scan_dt(low, w_dt, b_dt, dt, *, n_tokens):
+    """dt[t, c] = softplus(sum_r w_dt[c, r] * low[t, r] + b_dt[c]), 32-bit; low: a view whose first `rank` channels are
+    read; w_dt [channels, rank], b_dt [channels] 32-bit."""
+    channels, rank = w_dt.shape
+    _need(w_dt, "w_dt", torch.float32)
+    _need(b_dt, "b_dt", torch.float32, (channels,))
+    _need(dt, "dt", torch.float32, (None, channels))
+    if low.dim() != 2 or low.shape[1] < rank or low.stride(1) != 1 or low.dtype not in DTYPE_CODE or low.shape[0] < n_tokens \
+            or dt.shape[0] < n_tokens:
+        raise ShapeError("selective_scan_dt: low must hold the step's rows with at least `rank` contiguous channels")
+    _work(2.0 * n_tokens * channels * rank, 4.0 * n_tokens * channels)
+    _check(library().bt_selective_scan_dt(_ptr(low), c_longlong(low.stride(0)), _ptr(w_dt), _ptr(b_dt), _ptr(dt),
+                                          c_longlong(n_tokens), c_int(channels), c_int(rank), c_int(_code(low.dtype)),
+                                          _stream()))
+
+
+def selective_scan(x, z, dt, low, b_off, c_off, a_log, d_skip, state, slots, seq_start, out, *, n_seqs, out_scale=1.0):
+    """The scan S[c, n] <- exp(dt A) S + dt x B_n, y = (S . C + D x) * z sigmoid(z) * out_scale over the step's tokens of
+    every sequence (csrc/selective_scan.cu).  x, z, out: views [tokens, channels]; dt [tokens, channels] 32-bit; B and C
+    are the channels b_off.. and c_off.. of the rows of `low`; a_log [channels, n_state], d_skip [channels] 32-bit;
+    state [slots, channels, n_state] 32-bit, read and written at `slots[seq]`."""
+    channels, n_state = a_log.shape
+    _need(a_log, "a_log", torch.float32)
+    _need(d_skip, "d_skip", torch.float32, (channels,))
+    _need(state, "state", torch.float32, (None, channels, n_state))
+    _need(dt, "dt", torch.float32, (None, channels))
+    rows = dt.shape[0]
+    for name, t in (("x", x), ("z", z), ("out", out)):
+        _channels_view(t, "selective_scan: " + name, 0, channels)
+        if t.dtype != x.dtype:
+            raise ShapeError("selective_scan: x, z and out have one type")
+    if low.dim() != 2 or low.stride(1) != 1 or low.dtype != x.dtype or max(b_off, c_off) + n_state > low.shape[1] \
+            or min(b_off, c_off) < 0:
+        raise ShapeError("selective_scan: B and C must be channels of the rows of low, of x's type")
+    _work(6.0 * rows * channels * n_state, rows * channels * (3 * x.element_size() + 4) + 8.0 * n_seqs * channels * n_state)
+    _check(library().bt_selective_scan(_ptr(x), c_longlong(x.stride(0)), _ptr(z), c_longlong(z.stride(0)), _ptr(dt), _ptr(low),
+                                       c_longlong(low.stride(0)), c_int(b_off), c_int(c_off), _ptr(a_log), _ptr(d_skip),
+                                       _ptr(state), _ptr(slots), _ptr(seq_start), _ptr(out), c_longlong(out.stride(0)),
+                                       c_int(n_seqs), c_int(channels), c_int(n_state), c_float(out_scale),
+                                       c_int(_code(x.dtype)), _stream()))

@@ -125,3 +125,58 @@ class ParallelBlock(Block):
             ctx.ws.hold, ctx.side = held, step_side
         kernels.add_rows(residual, buffers, n_rows=n)
         ctx.ws.release(mark)
+
+
+class SandwichBlock(Block):
+    """A norm before and after each sublayer: x + norm1b(mixer(norm1(x))), then y + norm2b(feed_forward(norm2(y))).
+
+    The sublayers add into a zeroed 32-bit buffer instead of the stream; one kernel then norms the buffer, adds it to
+    the stream and, where another sublayer of the layer follows, norms the new row for it in the same pass
+    (csrc/rowwise.cu: rmsnorm_add).  All four norms are RMS norms of one eps."""
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm1b: Norm, norm2: Norm | None = None,
+                 feed_forward: FeedForward | None = None, norm2b: Norm | None = None):
+        if len({norm2 is None, feed_forward is None, norm2b is None}) != 1:
+            raise ValueError("a block has a feed-forward with both of its norms, or none of the three")
+        norms = [n for n in (norm1, norm1b, norm2, norm2b) if n is not None]
+        if any(getattr(n, "has_bias", True) or n.eps != norm1.eps or not hasattr(n, "offset") for n in norms):
+            raise ValueError("the norms around a sublayer are RMS norms with one eps")
+        self.norm1, self.mixer, self.norm1b = norm1, mixer, norm1b
+        self.norm2, self.feed_forward, self.norm2b = norm2, feed_forward, norm2b
+
+    def parts(self):
+        found = {"norm1": self.norm1, "mixer": self.mixer, "norm1b": self.norm1b}
+        for name, part in getattr(self.mixer, "parts", dict)().items():
+            found["mixer." + name] = part
+        if self.feed_forward is not None:
+            found.update({"norm2": self.norm2, "feed_forward": self.feed_forward, "norm2b": self.norm2b})
+        return found
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts().values())
+
+    def forward(self, ctx, residual, entry, owns_cache=True):
+        if getattr(ctx, "program", None) is not None:
+            from ..engine.program import ProgramUnsupported
+            raise ProgramUnsupported("norms after a sublayer have no phase in the fused step")
+        n, width = ctx.n_tokens, residual.shape[1]
+        mark = ctx.ws.mark()
+        branch = ctx.ws.take((n, width), torch.float32)
+        x = self.norm1.forward(ctx, residual, ctx.dtype, lazy=False)
+        inner = ctx.ws.mark()
+        branch.zero_()
+        self.mixer.forward(ctx, x, branch, entry, owns_cache)
+        ctx.ws.release(inner)
+        if self.feed_forward is None:
+            kernels.rmsnorm_add(branch, self.norm1b.t_weight, residual, self.norm1b.eps, n_rows=n)
+        else:
+            kernels.rmsnorm_add(branch, self.norm1b.t_weight, residual, self.norm1b.eps, n_rows=n,
+                                next_weight=self.norm2.t_weight, next_out=x)
+            branch.zero_()
+            self.feed_forward.forward(ctx, x, branch)
+            kernels.rmsnorm_add(branch, self.norm2b.t_weight, residual, self.norm2b.eps, n_rows=n)
+        ctx.ws.release(mark)

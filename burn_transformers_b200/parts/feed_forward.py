@@ -77,3 +77,37 @@ class GatedFeedForward(FeedForward):
         kernels.gated_activation(both, hidden, n_rows=n, activation=self.activation, limit=self.limit)
         linear(ctx, hidden, self.t_down_weight, None, residual, m=n, residual=residual, w_is_nk=True)
         ctx.ws.release(mark)
+
+
+class PolyNormFeedForward(FeedForward):
+    """down(act(up(x))) with a polynomial activation over the whole hidden row z:
+
+        act(z) = a N(z) + b N(z^2) + c N(z^3) + e,     N(v) = v / sqrt(mean(v^2) + eps)
+
+    powers element by element, (a, b, c, e) the four numbers of `act`; the activation is formed in 32-bit and rounded
+    once (csrc/rowwise.cu).  No biases; `up.weight` [inner, width] and `down.weight` [width, inner] (stored [out, in])."""
+
+    accepts_lazy_norm = True
+
+    def __init__(self, width: int, inner: int, eps: float, *, init_std: float = 0.02, down_init_std: float | None = None):
+        self.width, self.inner, self.eps = width, inner, float(eps)
+        self.init_std = init_std
+        self.down_init_std = init_std if down_init_std is None else down_init_std
+
+    def specs(self):
+        return {"up.weight": TensorSpec((self.inner, self.width), MATRIX, ("normal", self.init_std)),
+                "act": TensorSpec((4,), VECTOR, ("normal", 0.5)),
+                "down.weight": TensorSpec((self.width, self.inner), MATRIX, ("normal", self.down_init_std))}
+
+    def forward(self, ctx, x, residual):
+        if getattr(ctx, "program", None) is not None:
+            from ..engine.program import ProgramUnsupported
+            raise ProgramUnsupported("a polynomial activation has no phase in the fused step")
+        n = ctx.n_tokens
+        mark = ctx.ws.mark()
+        hidden = ctx.ws.take((n, self.inner), ctx.dtype)
+        linear(ctx, x, self.t_up_weight, None, hidden, m=n, w_is_nk=True)
+        shaped = ctx.ws.take((n, self.inner), ctx.dtype)
+        kernels.polynorm(hidden, self.t_act, shaped, self.eps, n_rows=n)
+        linear(ctx, shaped, self.t_down_weight, None, residual, m=n, residual=residual, w_is_nk=True)
+        ctx.ws.release(mark)

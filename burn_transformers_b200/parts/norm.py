@@ -40,15 +40,21 @@ class LayerNorm(Norm):
 
 
 class RmsNorm(Norm):
-    """x / sqrt(mean(x^2) + eps) * weight over the last axis, in 32-bit, eps inside the root; no shift."""
+    """x / sqrt(mean(x^2) + eps) * (offset + weight) over the last axis, in 32-bit, eps inside the root; no shift.
+    `offset` 1: the file keeps the gain minus one; the sum is formed once, in 32-bit, when the weights are bound."""
 
     has_bias = False
 
-    def __init__(self, width: int, eps: float):
-        self.width, self.eps = width, float(eps)
+    def __init__(self, width: int, eps: float, offset: float = 0.0):
+        self.width, self.eps, self.offset = width, float(eps), float(offset)
 
     def specs(self):
-        return {"weight": TensorSpec((self.width,), VECTOR, ("ones",))}
+        return {"weight": TensorSpec((self.width,), VECTOR, ("ones",) if self.offset == 0.0 else ("normal", 0.1))}
+
+    def bind(self, tensors):
+        if self.offset != 0.0:
+            tensors = {name: t.to(torch.float32) + self.offset for name, t in tensors.items()}
+        super().bind(tensors)
 
     def forward(self, ctx, x32, out_dtype, rows=None, n_rows=None, lazy=False):
         n = n_rows if n_rows is not None else ctx.n_tokens

@@ -62,3 +62,20 @@ class InterleavedRotary(PositionEncoding):
         heads = n_heads + n_kv_heads              # queries and keys lie side by side, values after them
         view = proj[:n, :heads * head_dim].view(n, heads, head_dim)
         self.rotate_vectors(ctx, view, view)
+
+
+class HalfSplitRotary(InterleavedRotary):
+    """The same turn with the other pairing: channel i < dims/2 of a vector goes with channel i + dims/2.  Its kernel
+    writes 32-bit vectors (a recurrence reads them), can scale the vectors from one index on afterwards (keys), and
+    copies the channels that follow the vectors in a row."""
+
+    def rotate_rows(self, ctx, src, dst, *, n_vecs: int, length: int, scaled_from=None, scale: float = 1.0,
+                    tail: int = 0) -> None:
+        kernels.rotary_half(src, dst, ctx.positions, self.inv_freq(src.device), n_tokens=ctx.n_tokens, n_vecs=n_vecs,
+                            length=length, dims=self.dims, scaled_from=scaled_from, scale=scale, tail=tail)
+
+    def rotate_vectors(self, ctx, src, dst) -> None:
+        raise NotImplementedError("the half-split rotation writes 32-bit rows: use rotate_rows")
+
+    def rotate(self, ctx, proj, n_heads, n_kv_heads, head_dim) -> None:
+        raise NotImplementedError("the half-split rotation writes 32-bit rows: use rotate_rows")
