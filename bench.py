@@ -1,7 +1,7 @@
 """Decode and prefill throughput of GPT-2 (random weights, synthetic tokens) on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--points all|small] [--profile]
-    python bench.py --arch sovozen|gokezen [--sizes small,medium]
+    python bench.py --arch sovozen|gokezen|rakarax [--sizes small,medium]
 
 A step is one decode step of a batch of 8 sequences of GPT-2 small.  The run prints one JSON line: `value` is decoded
 tokens per second, timed on the device with CUDA events over exactly K steps; `e2e` is the same through the public
@@ -395,12 +395,38 @@ def gokezen(size: str) -> dict:
             "layers": layers, "loop": {"start": stored // 4, "stop": stored // 4 + n_layer - stored, "times": 2}}
 
 
-ARCH_PAIRS = {"sovozen": (sovozen, "gpt2", gpt2), "gokezen": (gokezen, "sovozen", sovozen)}
+def rakarax(size: str) -> dict:
+    """A Rakarax with as many layers, the width and the heads of GPT-2 `size`: two of every three layers a windowed
+    attention behind a convolution of 4 taps (a key head for every four query heads, window 512, talking heads) beside a
+    selective scan (inner = 2 x width, 16 state indices, a step-size rank of width / 16); every third layer a retention
+    (the layer before the last runs with an earlier retention's tensors); dense feed-forwards with the polynomial
+    activation and GPT-2's weight count (2 x ff x width = 8 x width^2)."""
+    n_layer, width, heads = {"small": (12, 768, 12), "medium": (24, 1024, 16)}[size]
+    dim = 64
+    mlp = {"kind": "dense", "ff": 4 * width}
+    parallel = {"type": "parallel", "mlp": mlp,
+                "mixer": {"left": {"heads": heads, "kv_heads": heads // 4, "dim": dim, "vdim": dim, "conv": 4,
+                                   "scale": dim ** -0.5, "softcap": 30.0, "mask": {"size": 512}},
+                          "left_scale": 1.0,
+                          "right": {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4},
+                          "right_scale": 1.0}}
+    retention = {"type": "retention", "mlp": mlp,
+                 "mixer": {"heads": heads, "dim": dim, "vdim": dim, "rot": {"dims": dim, "base": 10000.0},
+                           "decay": [1.0 - 2.0 ** -(3 + h % 6) for h in range(heads)]}}
+    layers = [dict(retention) if i % 3 == 2 else dict(parallel) for i in range(n_layer)]
+    layers[n_layer - 1] = dict(layers[2], weights_of=2)
+    return {"architecture": "Rakarax", "vocab": 50257, "width": width, "max_positions": 2048, "norm": {"eps": 1e-5},
+            "layers": layers}
+
+
+ARCH_PAIRS = {"sovozen": (sovozen, "gpt2", gpt2), "gokezen": (gokezen, "sovozen", sovozen),
+              "rakarax": (rakarax, "gokezen", gokezen)}
 
 
 def run_arch_compare(args):
-    """--arch sovozen | gokezen: prefill and decode throughput of that design beside the library's closest other
-    model at the same width and depth (GPT-2 for Sovozen, Sovozen for Gokezen; random weights, bfloat16), and where each
+    """--arch sovozen | gokezen | rakarax: prefill and decode throughput of that design beside the library's closest
+    other model at the same width and depth (GPT-2 for Sovozen, Sovozen for Gokezen, Gokezen for Rakarax; random weights,
+    bfloat16), and where each
     spends a prefill and a decode step, kernel by kernel, against the measured peaks.  One JSON line; the default
     workload of this file is untouched."""
     import numpy as np
@@ -621,10 +647,10 @@ def main() -> int:
     parser.add_argument("--profile", action="store_true",
                         help="print where a prefill and a decode step spend their time, kernel by kernel, instead")
     parser.add_argument("--model", choices=["small", "medium", "xl"], default="small", help="the model --profile looks at")
-    parser.add_argument("--arch", choices=["gpt2", "sovozen", "gokezen"], default="gpt2",
-                        help="sovozen, gokezen: measure that design beside the closest other model of equal width and "
+    parser.add_argument("--arch", choices=["gpt2", "sovozen", "gokezen", "rakarax"], default="gpt2",
+                        help="sovozen, gokezen, rakarax: measure that design beside the closest other model of equal width and "
                              "depth instead (see --sizes)")
-    parser.add_argument("--sizes", default="small,medium", help="with --arch sovozen | gokezen: which widths (small, medium)")
+    parser.add_argument("--sizes", default="small,medium", help="with --arch sovozen | gokezen | rakarax: which widths (small, medium)")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate (Cargo.toml only): pip "

@@ -72,10 +72,11 @@ class KvGroup:
     pool: _PageBooks
     k: torch.Tensor               # [layers, pages, kv_heads, PAGE_SIZE, head_dim]
     v: torch.Tensor
+    whole: bool = False           # the table reaches the longest sequence: its pages never come round
 
     @property
     def is_ring(self) -> bool:
-        return self.spec.window is not None
+        return self.spec.window is not None and not self.whole
 
 
 class CacheBank:
@@ -112,7 +113,8 @@ class CacheBank:
             v_shape = shape if spec.has_values else (len(entries), 0, spec.n_kv_heads, PAGE_SIZE, spec.head_dim)
             group = KvGroup(spec, entries, table_len, _PageBooks(self, len(self.groups), n_pages),
                             torch.zeros(shape, dtype=kv_dtype, device=self.device),
-                            torch.zeros(v_shape, dtype=kv_dtype, device=self.device))
+                            torch.zeros(v_shape, dtype=kv_dtype, device=self.device),
+                            whole=table_len >= self.table_width)
             for layer, entry in enumerate(entries):
                 self._entry_group[entry] = (len(self.groups), layer)
             self.groups.append(group)
