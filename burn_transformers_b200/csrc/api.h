@@ -146,14 +146,14 @@ int bt_talking_attention(const void* q, long long q_row_stride, const void* k, c
                          long long gate_row_stride, void* out, long long out_row_stride, const int* seq_start,
                          const int* past_len, const float* temp, const float* slope, const float* talk, int n_seqs,
                          int max_new, int n_heads, int n_kv_heads, int head_dim, float scale, float cap, int window,
-                         float out_scale, int dtype, cudaStream_t stream);
+                         float out_scale, int plain, int n_split, float* parts, int dtype, cudaStream_t stream);
 int bt_selective_scan_dt(const void* low, long long low_row_stride, const float* w_dt, const float* b_dt, float* dt,
                          long long n_tokens, int channels, int rank, int dtype, cudaStream_t stream);
 int bt_selective_scan(const void* x, long long x_row_stride, const void* z, long long z_row_stride, const float* dt,
                       const void* low, long long low_row_stride, int b_off, int c_off, const float* a_log,
                       const float* d_skip, float* state, const int* slots, const int* seq_start, void* out,
-                      long long out_row_stride, int n_seqs, int channels, int n_state, float out_scale, int dtype,
-                      cudaStream_t stream);
+                      long long out_row_stride, int n_seqs, int channels, int n_state, float out_scale, int piece,
+                      int max_pieces, float* ends, int dtype, cudaStream_t stream);
 int bt_rotary_interleaved(const void* src, long long src_row_stride, int src_vec_stride, void* dst,
                           long long dst_row_stride, int dst_vec_stride, const int* positions, const float* inv_freq,
                           int n_tokens, int n_vecs, int len, int dims, int dtype, cudaStream_t stream);

@@ -8,6 +8,14 @@
 // of other rows.  Step sizes, decays, the state and all sums are 32-bit.  A channel belongs to LANES adjacent lanes,
 // each with NS of the `n_state` indices in registers for all tokens of the step; their partial sums meet by shuffles.
 // The tokens of a run are staged in shared memory TT at a time.  state: [slots][channels][n_state].
+//
+// A long run is cut into pieces of `piece` tokens that run side by side.  A first launch (ENDS) runs every piece but a
+// sequence's last from a zero state and leaves, per channel, what it ends with, E[n], and the sum of its step sizes, d;
+// the state after the piece is then exp(A[n] d) * (state before it) + E[n], since the recurrence is linear in the state
+// and its decays multiply to exp(A[n] * sum dt).  The second launch gives every piece its own block, which first walks
+// the earlier pieces' (E, d) from the sequence's stored state to its own start and then runs its tokens as the single
+// run would; the last piece writes the state back.  `ends`: [pieces of the step][channels][n_state + 1], where the
+// pieces of sequence s begin at first_row(s) / piece + s.
 #include "common.cuh"
 
 namespace bt {
@@ -52,13 +60,14 @@ selective_scan_dt_kernel(const T* __restrict__ low, long long low_row_stride, co
   }
 }
 
-template <typename T, int NS, int LANES>
+template <typename T, int NS, int LANES, bool ENDS>
 __global__ void __launch_bounds__(SS_THREADS)
 selective_scan_kernel(const T* __restrict__ x, long long x_row_stride, const T* __restrict__ z, long long z_row_stride,
                       const float* __restrict__ dt, const T* __restrict__ low, long long low_row_stride, int b_off,
                       int c_off, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                       float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ seq_start,
-                      T* __restrict__ out, long long out_row_stride, int channels, int n_state, float out_scale) {
+                      T* __restrict__ out, long long out_row_stride, int channels, int n_state, float out_scale, int piece,
+                      float* __restrict__ ends) {
   constexpr int CPB = SS_THREADS / LANES;      // channels per block
   extern __shared__ float sm[];
   float* bc_s = sm;                            // [SS_TT][2 * n_state]
@@ -75,12 +84,30 @@ selective_scan_kernel(const T* __restrict__ x, long long x_row_stride, const T* 
   for (int i = 0; i < NS; ++i) a[i] = owns && n0 + i < n_state ? -expf(a_log[(long long)c * n_state + n0 + i]) : 0.f;
   const float skip = owns ? d_skip[c] : 0.f;
   pdl_wait();
-  const int first = seq_start[seq], n_new = seq_start[seq + 1] - first;
+  const int first = seq_start[seq], n_all = seq_start[seq + 1] - first;
+  // this block's piece of the run: tokens [t_lo, t_hi); the whole run when piece == 0
+  const int n_pieces = piece > 0 ? (n_all + piece - 1) / piece : 1;
+  const int my_piece = piece > 0 ? (int)blockIdx.z : 0;
+  if (my_piece >= n_pieces - (ENDS ? 1 : 0)) return;
+  const int t_lo = my_piece * piece, t_hi = piece > 0 ? min(n_all, t_lo + piece) : n_all;
+  const bool last_piece = my_piece == n_pieces - 1;
+  const long long es = (long long)channels * (n_state + 1);
+  float* e_base = piece > 0 ? ends + ((long long)(first / piece + seq)) * es + (long long)(owns ? c : 0) * (n_state + 1) : nullptr;
   float* s_base = state + ((long long)slots[seq] * channels + (owns ? c : 0)) * n_state;
+  float dt_sum = 0.f;
 #pragma unroll
-  for (int i = 0; i < NS; ++i) s[i] = owns && n0 + i < n_state ? s_base[n0 + i] : 0.f;
-  for (int t0 = 0; t0 < n_new; t0 += SS_TT) {
-    const int nt = min(SS_TT, n_new - t0);
+  for (int i = 0; i < NS; ++i) s[i] = !ENDS && owns && n0 + i < n_state ? s_base[n0 + i] : 0.f;
+  if (!ENDS && owns) {
+    for (int j = 0; j < my_piece; ++j) {
+      const float* e = e_base + (long long)j * es;
+      const float d = e[n_state];
+#pragma unroll
+      for (int i = 0; i < NS; ++i)
+        if (n0 + i < n_state) s[i] = fmaf(expf(d * a[i]), s[i], e[n0 + i]);
+    }
+  }
+  for (int t0 = t_lo; t0 < t_hi; t0 += SS_TT) {
+    const int nt = min(SS_TT, t_hi - t0);
     __syncthreads();
     for (int i = threadIdx.x; i < nt * 2 * n_state; i += SS_THREADS) {
       const int t = i / (2 * n_state), n = i - t * 2 * n_state;
@@ -109,8 +136,12 @@ selective_scan_kernel(const T* __restrict__ x, long long x_row_stride, const T* 
           y = fmaf(s[i], ct_[i], y);
         }
       }
+      if (!ENDS) {
 #pragma unroll
-      for (int o = 1; o < LANES; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+        for (int o = 1; o < LANES; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+      }
+      dt_sum += d;
+      if (ENDS) continue;
       if (owns && part == 0) {
         const float zv = z_s[t * CPB + c_local];
         const float r = (y + skip * xv) * (zv / (1.f + expf(-zv))) * out_scale;
@@ -118,7 +149,17 @@ selective_scan_kernel(const T* __restrict__ x, long long x_row_stride, const T* 
       }
     }
   }
-  if (owns) {
+  if (ENDS) {
+    if (owns) {
+      float* e = e_base + (long long)my_piece * es;
+#pragma unroll
+      for (int i = 0; i < NS; ++i)
+        if (n0 + i < n_state) e[n0 + i] = s[i];
+      if (part == 0) e[n_state] = dt_sum;
+    }
+    return;
+  }
+  if (owns && last_piece) {
 #pragma unroll
     for (int i = 0; i < NS; ++i)
       if (n0 + i < n_state) s_base[n0 + i] = s[i];
@@ -129,7 +170,8 @@ template <typename T>
 static int launch_selective_scan(const T* x, long long xs, const T* z, long long zs, const float* dt, const T* low,
                                  long long ls, int b_off, int c_off, const float* a_log, const float* d_skip, float* state,
                                  const int* slots, const int* seq_start, T* out, long long os, int n_seqs, int channels,
-                                 int n_state, float out_scale, cudaStream_t stream) {
+                                 int n_state, float out_scale, int piece, int max_pieces, float* ends,
+                                 cudaStream_t stream) {
   int ns, lanes;
   if (n_state <= 16) { ns = 4; lanes = 4; }
   else if (n_state <= 32) { ns = 8; lanes = 4; }
@@ -139,12 +181,18 @@ static int launch_selective_scan(const T* x, long long xs, const T* z, long long
   else { ns = 16; lanes = 32; }
   BT_CHECK(n_state <= 512, "selective_scan: %d state indices a channel; the kernel takes up to 512", n_state);
   const int cpb = SS_THREADS / lanes;
-  const dim3 grid((channels + cpb - 1) / cpb, n_seqs);
+  const dim3 grid((channels + cpb - 1) / cpb, n_seqs, piece > 0 ? max_pieces : 1);
   const size_t smem = sizeof(float) * ((size_t)SS_TT * 2 * n_state + 3 * (size_t)SS_TT * cpb);
 #define BT_SS(NS, LANES)                                                                                              \
-  BT_PDL_OK("selective_scan", launch_pdl(selective_scan_kernel<T, NS, LANES>, grid, dim3(SS_THREADS), smem, stream, 1, x, \
-                                         xs, z, zs, dt, low, ls, b_off, c_off, a_log, d_skip, state, slots, seq_start,  \
-                                         out, os, channels, n_state, out_scale))
+  do {                                                                                                                \
+    if (piece > 0)                                                                                                    \
+      BT_PDL_OK("selective_scan", launch_pdl(selective_scan_kernel<T, NS, LANES, true>, grid, dim3(SS_THREADS), smem, \
+                                             stream, 1, x, xs, z, zs, dt, low, ls, b_off, c_off, a_log, d_skip, state, \
+                                             slots, seq_start, out, os, channels, n_state, out_scale, piece, ends));   \
+    BT_PDL_OK("selective_scan", launch_pdl(selective_scan_kernel<T, NS, LANES, false>, grid, dim3(SS_THREADS), smem,   \
+                                           stream, 1, x, xs, z, zs, dt, low, ls, b_off, c_off, a_log, d_skip, state,   \
+                                           slots, seq_start, out, os, channels, n_state, out_scale, piece, ends));     \
+  } while (0)
   if (ns == 4) BT_SS(4, 4);
   else if (ns == 8) BT_SS(8, 4);
   else if (lanes == 4) BT_SS(16, 4);
@@ -183,23 +231,29 @@ extern "C" int bt_selective_scan_dt(const void* low, long long low_row_stride, c
   return 0;
 }
 
-// x, z, out: first channel of [tokens, channels] views; low: the rows that hold B at b_off and C at c_off
+// x, z, out: first channel of [tokens, channels] views; low: the rows that hold B at b_off and C at c_off.
+// piece > 0: runs are cut into pieces of `piece` tokens (a multiple of 16), none has more than max_pieces, and `ends`
+// holds (n_tokens / piece + n_seqs + 1) * channels * (n_state + 1) floats; piece == 0: a block walks a whole run.
 extern "C" int bt_selective_scan(const void* x, long long x_row_stride, const void* z, long long z_row_stride,
                                  const float* dt, const void* low, long long low_row_stride, int b_off, int c_off,
                                  const float* a_log, const float* d_skip, float* state, const int* slots,
                                  const int* seq_start, void* out, long long out_row_stride, int n_seqs, int channels,
-                                 int n_state, float out_scale, int dtype, cudaStream_t stream) {
+                                 int n_state, float out_scale, int piece, int max_pieces, float* ends, int dtype,
+                                 cudaStream_t stream) {
   using namespace bt;
+  BT_CHECK(piece == 0 || (piece % SS_TT == 0 && max_pieces > 0 && max_pieces <= 65535 && ends != nullptr),
+           "selective_scan: pieces of %d tokens (a multiple of %d), at most %d a run, need scratch", piece, SS_TT, max_pieces);
   BT_CHECK(channels > 0 && n_state > 0 && n_seqs >= 0 && n_seqs <= 65535, "selective_scan: bad sizes seqs=%d channels=%d "
            "state=%d", n_seqs, channels, n_state);
   if (n_seqs == 0) return 0;
   if (dtype == kF32)
     return launch_selective_scan((const float*)x, x_row_stride, (const float*)z, z_row_stride, dt, (const float*)low,
                                  low_row_stride, b_off, c_off, a_log, d_skip, state, slots, seq_start, (float*)out,
-                                 out_row_stride, n_seqs, channels, n_state, out_scale, stream);
+                                 out_row_stride, n_seqs, channels, n_state, out_scale, piece, max_pieces, ends, stream);
   if (dtype == kBF16)
     return launch_selective_scan((const __nv_bfloat16*)x, x_row_stride, (const __nv_bfloat16*)z, z_row_stride, dt,
                                  (const __nv_bfloat16*)low, low_row_stride, b_off, c_off, a_log, d_skip, state, slots,
-                                 seq_start, (__nv_bfloat16*)out, out_row_stride, n_seqs, channels, n_state, out_scale, stream);
+                                 seq_start, (__nv_bfloat16*)out, out_row_stride, n_seqs, channels, n_state, out_scale, piece,
+                                 max_pieces, ends, stream);
   return fail("selective_scan: unknown dtype %d", dtype);
 }

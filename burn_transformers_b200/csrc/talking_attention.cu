@@ -15,6 +15,13 @@
 
 namespace bt {
 
+// talking_attention_mma.cu
+int talking_attention_mma(const void* q, long long q_row_stride, const KvView& view, const void* gate,
+                          long long gate_row_stride, void* out, long long out_row_stride, const int* seq_start,
+                          const int* past_len, const float* temp, const float* slope, const float* talk, int n_seqs,
+                          int max_new, int n_heads, int n_kv_heads, int head_dim, float scale, float cap, int window,
+                          float out_scale, int n_split, float* parts, cudaStream_t stream, bool* taken);
+
 template <typename T, int BQ, int NV>
 __global__ void __launch_bounds__(1024)
 talking_attention_kernel(const T* __restrict__ q, long long q_row_stride, KvView kv, const T* __restrict__ gate,
@@ -180,13 +187,16 @@ static int launch_talking(const T* q, long long q_row_stride, const KvView& view
 
 // q, gate, out: the first channel of [tokens, heads * head_dim] views (rows *_row_stride elements apart).  kv_table
 // null: keys and values are rows of the step itself (k, v point at their first channel of row 0, rows kv_row_stride
-// apart); else pages.  temp, slope [heads] and talk [heads, heads] are 32-bit and may be null.
+// apart); else pages.  temp, slope [heads] and talk [heads, heads] are 32-bit and may be null.  bfloat16 rows go to the
+// tensor-core form (talking_attention_mma.cu) where it takes them, unless `plain` asks for the kernel of this file; there
+// a step of at most 16 tokens a sequence may share every sequence's keys among n_split blocks that meet in `parts`.
 extern "C" int bt_talking_attention(const void* q, long long q_row_stride, const void* k, const void* v, const int* kv_table,
                                     int table_stride, int table_len, int page_size, long long kv_row_stride,
                                     const void* gate, long long gate_row_stride, void* out, long long out_row_stride,
                                     const int* seq_start, const int* past_len, const float* temp, const float* slope,
                                     const float* talk, int n_seqs, int max_new, int n_heads, int n_kv_heads, int head_dim,
-                                    float scale, float cap, int window, float out_scale, int dtype, cudaStream_t stream) {
+                                    float scale, float cap, int window, float out_scale, int plain, int n_split,
+                                    float* parts, int dtype, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_heads > 0 && n_heads <= 32 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
            "talking_attention: %d query heads (at most 32) over %d key heads", n_heads, n_kv_heads);
@@ -204,6 +214,13 @@ extern "C" int bt_talking_attention(const void* q, long long q_row_stride, const
     BT_TA_GO(float, 4);
   }
   if (dtype == kBF16) {
+    if (!plain) {
+      bool taken = false;
+      const int rc = talking_attention_mma(q, q_row_stride, view, gate, gate_row_stride, out, out_row_stride, seq_start,
+                                           past_len, temp, slope, talk, n_seqs, max_new, n_heads, n_kv_heads, head_dim,
+                                           scale, cap, window, out_scale, n_split, parts, stream, &taken);
+      if (taken || rc) return rc;
+    }
     if (max_new == 1) BT_TA_GO(__nv_bfloat16, 1);
     BT_TA_GO(__nv_bfloat16, 4);
   }

@@ -1218,15 +1218,42 @@ def short_conv(src, weight, bias, state, slots, seq_start, token_seq, out, *, n_
                                    c_int(1 if activation == "swish" else 0), c_int(norm_group), c_float(eps), _stream()))
 
 
+TALK_SPLIT_ROWS = 16      # a step that brings at most this many tokens a sequence may share a sequence's keys among blocks
+TALK_KEY_TILE = 32
+N_SMS = 148               # of a B200
+
+
+def talking_attention_split(n_seqs: int, max_new: int, n_heads: int, head_dim: int, window: int, ctx_bound: int):
+    """Among how many blocks the tensor-core form shares the keys of every sequence in a step of `n_seqs` sequences that
+    brings at most `max_new` tokens to each and leaves none longer than `ctx_bound`, and the 32-bit numbers of scratch
+    they meet in: enough blocks to fill the GPU about twice, no more than a sequence has tiles of keys.  (1, 0): no
+    sharing."""
+    if max_new > TALK_SPLIT_ROWS or n_seqs <= 0:
+        return 1, 0
+    seen = min(ctx_bound, window + max_new - 1) if window else ctx_bound
+    tiles = -(-seen // TALK_KEY_TILE) + 1
+    n_split = max(1, min(tiles, -(-2 * N_SMS // n_seqs)))
+    if n_split == 1:
+        return 1, 0
+    return n_split, n_seqs * n_split * n_heads * max_new * (head_dim + 2)
+
+
 def talking_attention(q, out, seq_start, past_len, *, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale, window=0,
                       cap=0.0, temp=None, slope=None, talk=None, gate=None, out_scale=1.0, k=None, v=None, k_pool=None,
-                      v_pool=None, table=None, table_len=0):
+                      v_pool=None, table=None, table_len=0, plain=False, n_split=1, parts=None):
     """Causal (windowed) attention over all heads of a token at once (csrc/talking_attention.cu):
     raw_g = cap tanh((q_g . k_g) scale temp[g] / cap) - slope[g] (i - j), s_h = sum_g talk[h, g] raw_g, softmax over the
     visible keys, the value mix, times sigmoid(gate) and out_scale.  q, gate, out: views [tokens, heads * head_dim];
     keys and values either views [tokens, kv_heads * head_dim] of the step's own rows (`k`, `v`: sequences that start in
-    this step) or the pages of the cache."""
+    this step) or the pages of the cache.  bfloat16 rows whose heads have a multiple of 8 channels (up to 128) run on
+    tensor cores (csrc/talking_attention_mma.cu) unless `plain` is set; 32-bit rows and the rest in plain arithmetic.
+    With `n_split` > 1 and `parts` (32-bit, as talking_attention_split says) that form shares every sequence's keys among
+    n_split blocks."""
     width = n_heads * head_dim
+    if n_split > 1:
+        if max_new > TALK_SPLIT_ROWS or parts is None or parts.dtype != torch.float32 or not parts.is_contiguous() \
+                or parts.numel() < n_seqs * n_split * n_heads * max_new * (head_dim + 2):
+            raise ShapeError("talking_attention: sharing the keys among blocks needs a step of few tokens and scratch")
     for name, t in (("q", q), ("out", out)) + ((("gate", gate),) if gate is not None else ()):
         _channels_view(t, "talking_attention: " + name, 0, width)
         if t.dtype != q.dtype:
@@ -1256,7 +1283,8 @@ def talking_attention(q, out, seq_start, past_len, *, n_seqs, max_new, n_heads, 
         c_longlong(kv_stride), _ptr(gate), c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out),
         c_longlong(out.stride(0)), _ptr(seq_start), _ptr(past_len), _ptr(temp), _ptr(slope), _ptr(talk), c_int(n_seqs),
         c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_float(cap), c_int(window),
-        c_float(out_scale), c_int(_code(q.dtype)), _stream()))
+        c_float(out_scale), c_int(1 if plain else 0), c_int(n_split if n_split > 1 else 1),
+        _ptr(parts) if n_split > 1 else c_void_p(0), c_int(_code(q.dtype)), _stream()))
 
 
 def selective_scan_dt(low, w_dt, b_dt, dt, *, n_tokens):
@@ -1275,11 +1303,28 @@ def selective_scan_dt(low, w_dt, b_dt, dt, *, n_tokens):
                                           _stream()))
 
 
-def selective_scan(x, z, dt, low, b_off, c_off, a_log, d_skip, state, slots, seq_start, out, *, n_seqs, out_scale=1.0):
+SCAN_PIECE = 64          # tokens of a run that one block of the selective scan walks, while a run has at most ...
+SCAN_MAX_PIECES = 64     # ... this many pieces
+
+
+def selective_scan_pieces(max_new: int, n_tokens: int, n_seqs: int, channels: int, n_state: int):
+    """How the selective scan cuts the runs of a step whose longest has `max_new` tokens: (tokens a piece, the most
+    pieces of a run, 32-bit numbers of scratch).  (0, 1, 0): every run is one piece and needs no scratch."""
+    if max_new <= SCAN_PIECE:
+        return 0, 1, 0
+    piece = max(SCAN_PIECE, -(-max_new // SCAN_MAX_PIECES))
+    piece = (piece + 15) // 16 * 16
+    return piece, -(-max_new // piece), (n_tokens // piece + n_seqs + 1) * channels * (n_state + 1)
+
+
+def selective_scan(x, z, dt, low, b_off, c_off, a_log, d_skip, state, slots, seq_start, out, *, n_seqs, out_scale=1.0,
+                   max_new=0, scratch=None):
     """The scan S[c, n] <- exp(dt A) S + dt x B_n, y = (S . C + D x) * z sigmoid(z) * out_scale over the step's tokens of
     every sequence (csrc/selective_scan.cu).  x, z, out: views [tokens, channels]; dt [tokens, channels] 32-bit; B and C
     are the channels b_off.. and c_off.. of the rows of `low`; a_log [channels, n_state], d_skip [channels] 32-bit;
-    state [slots, channels, n_state] 32-bit, read and written at `slots[seq]`."""
+    state [slots, channels, n_state] 32-bit, read and written at `slots[seq]`.  With `max_new` (the longest run of the
+    step) and `scratch` (32-bit, as many numbers as selective_scan_pieces says) long runs are cut into pieces that run
+    side by side; without them a block walks a whole run."""
     channels, n_state = a_log.shape
     _need(a_log, "a_log", torch.float32)
     _need(d_skip, "d_skip", torch.float32, (channels,))
@@ -1293,9 +1338,15 @@ def selective_scan(x, z, dt, low, b_off, c_off, a_log, d_skip, state, slots, seq
     if low.dim() != 2 or low.stride(1) != 1 or low.dtype != x.dtype or max(b_off, c_off) + n_state > low.shape[1] \
             or min(b_off, c_off) < 0:
         raise ShapeError("selective_scan: B and C must be channels of the rows of low, of x's type")
+    piece, max_pieces, need = selective_scan_pieces(max_new, rows, n_seqs, channels, n_state) if scratch is not None \
+        else (0, 1, 0)
+    if piece:
+        if scratch.dtype != torch.float32 or not scratch.is_contiguous() or scratch.numel() < need:
+            raise ShapeError(f"selective_scan: runs of up to {max_new} tokens in pieces need {need} floats of scratch")
     _work(6.0 * rows * channels * n_state, rows * channels * (3 * x.element_size() + 4) + 8.0 * n_seqs * channels * n_state)
     _check(library().bt_selective_scan(_ptr(x), c_longlong(x.stride(0)), _ptr(z), c_longlong(z.stride(0)), _ptr(dt), _ptr(low),
                                        c_longlong(low.stride(0)), c_int(b_off), c_int(c_off), _ptr(a_log), _ptr(d_skip),
                                        _ptr(state), _ptr(slots), _ptr(seq_start), _ptr(out), c_longlong(out.stride(0)),
-                                       c_int(n_seqs), c_int(channels), c_int(n_state), c_float(out_scale),
+                                       c_int(n_seqs), c_int(channels), c_int(n_state), c_float(out_scale), c_int(piece),
+                                       c_int(max_pieces), _ptr(scratch) if piece else c_void_p(0),
                                        c_int(_code(x.dtype)), _stream()))

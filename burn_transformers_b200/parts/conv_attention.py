@@ -102,6 +102,12 @@ class TalkingConvAttention(Mixer):
         common = dict(n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
                       head_dim=self.dim, scale=self.scale, window=self.window or 0, cap=self.softcap, temp=self.t_temp,
                       slope=self.slope, talk=self.t_talk, gate=proj[:, self.conv_width:])
+        if dtype == torch.bfloat16:
+            # few tokens a sequence: the keys of each are shared among blocks
+            n_split, need = kernels.talking_attention_split(ctx.n_seqs, ctx.max_new, self.n_heads, self.dim,
+                                                            self.window or 0, ctx.ctx_bound)
+            if n_split > 1:
+                common.update(n_split=n_split, parts=ctx.ws.take((need,), torch.float32))
         if ctx.fresh:
             # every sequence starts at position 0: keys and values are the step's own rows
             kernels.talking_attention(qkv[:, :self.q_width], mixed, ctx.seq_start, ctx.past_len,

@@ -95,8 +95,12 @@ class SelectiveScan(Mixer):
         dt = ctx.ws.take((n, inner), torch.float32)
         kernels.selective_scan_dt(low, self.t_dt_weight, self.t_dt_bias, dt, n_tokens=n)
         y = ctx.ws.take((n, inner), dtype)
+        scratch = None
+        need = kernels.selective_scan_pieces(ctx.max_new, n, ctx.n_seqs, inner, self.n_state)[2]
+        if need:
+            scratch = ctx.ws.take((need,), torch.float32)
         kernels.selective_scan(xc, xz[:, inner:], dt, low, self.dt_rank, self.dt_rank + self.n_state, self.t_A_log,
                                self.t_D, ctx.cache.state(entry, "scan"), ctx.slots, ctx.seq_start, y, n_seqs=ctx.n_seqs,
-                               out_scale=self.out_scale)
+                               out_scale=self.out_scale, max_new=ctx.max_new, scratch=scratch)
         linear(ctx, y, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)
         ctx.ws.release(mark)

@@ -130,10 +130,13 @@ def slopes(H):
     return dev(np.array([2.0 ** (-8.0 * (a + 1) / H) for a in range(H)]))
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+KINDS = [("float32", False), ("bfloat16", False), ("bfloat16", True)]      # (type of the rows, the plain kernel only)
+
+
+@pytest.mark.parametrize("dtype, plain_kernel", KINDS)
 @pytest.mark.parametrize("H, G, D, window", [(6, 2, 24, 40), (4, 4, 32, 0), (1, 1, 14, 5), (5, 1, 12, 33), (2, 1, 128, 70),
-                                             (3, 3, 72, 1), (8, 2, 64, 72), (2, 2, 200, 64)])
-def test_talking_attention_over_the_steps_own_rows(dtype, H, G, D, window):
+                                             (3, 3, 72, 1), (8, 2, 64, 72), (2, 2, 200, 64), (12, 4, 48, 31), (20, 5, 16, 97)])
+def test_talking_attention_over_the_steps_own_rows(dtype, plain_kernel, H, G, D, window):
     rng = np.random.default_rng(H * D + window)
     lengths = [75, 1, 130, 6]
     starts, _ = step_tables(lengths)
@@ -148,7 +151,7 @@ def test_talking_attention_over_the_steps_own_rows(dtype, H, G, D, window):
     kernels.talking_attention(t_rows[:, :H * D], out, ints(starts), ints([0] * 4), n_seqs=4, max_new=max(lengths), n_heads=H,
                               n_kv_heads=G, head_dim=D, scale=scale, window=window, cap=cap, temp=dev(temp), slope=slopes(H),
                               talk=dev(talk), gate=dev(gate, DT[dtype]), out_scale=0.7, k=t_rows[:, H * D:(H + G) * D],
-                              v=t_rows[:, (H + G) * D:])
+                              v=t_rows[:, (H + G) * D:], plain=plain_kernel)
     got = out.double().cpu().numpy()
     t32 = lambda a: a.astype(np.float32).astype(np.float64)
     for lo, hi in zip(starts[:-1], starts[1:]):
@@ -159,10 +162,11 @@ def test_talking_attention_over_the_steps_own_rows(dtype, H, G, D, window):
         close(got[lo:hi], want, TOL[dtype])
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("new", [1, 9])
-@pytest.mark.parametrize("H, G, D, window", [(6, 2, 24, 40), (4, 4, 32, 0), (3, 1, 16, 100), (2, 2, 72, 64), (8, 2, 64, 72)])
-def test_talking_attention_over_scattered_pages(dtype, new, H, G, D, window):
+@pytest.mark.parametrize("dtype, plain_kernel", KINDS)
+@pytest.mark.parametrize("new", [1, 9, 40])
+@pytest.mark.parametrize("H, G, D, window", [(6, 2, 24, 40), (4, 4, 32, 0), (3, 1, 16, 100), (2, 2, 72, 64), (8, 2, 64, 72),
+                                             (10, 5, 40, 130)])
+def test_talking_attention_over_scattered_pages(dtype, plain_kernel, new, H, G, D, window):
     """Sequences that already hold tokens: keys and values lie in pages in no order; a window's pages are a ring that
     has come round."""
     rng = np.random.default_rng(H + D + window + new)
@@ -193,19 +197,37 @@ def test_talking_attention_over_scattered_pages(dtype, new, H, G, D, window):
     temp, talk = rng.standard_normal(H) + 1.5, rng.standard_normal((H, H)) * 0.5 + np.eye(H)
     out = torch.zeros((total, H * D), dtype=DT[dtype], device=DEV)
     scale, cap = 1.2 * D ** -0.5, 9.0
-    kernels.talking_attention(dev(q, DT[dtype]), out, ints(starts), ints(pasts), n_seqs=n_seqs, max_new=new, n_heads=H,
-                              n_kv_heads=G, head_dim=D, scale=scale, window=window, cap=cap, temp=dev(temp), slope=slopes(H),
-                              talk=dev(talk), k_pool=k_pool, v_pool=v_pool, table=ints(pages), table_len=table_len)
-    got = out.double().cpu().numpy()
     t32 = lambda a: a.astype(np.float32).astype(np.float64)
-    for s, (lo, hi) in enumerate(zip(starts[:-1], starts[1:])):
-        want = plain_talking(q[lo:hi].reshape(-1, H, D), keys[s], values[s], None, t32(temp), t32(talk), scale, cap, window,
-                             1.0, past=pasts[s])
-        close(got[lo:hi], want, TOL[dtype], f"sequence {s}: ")
+    wants = [plain_talking(q[lo:hi].reshape(-1, H, D), keys[s], values[s], None, t32(temp), t32(talk), scale, cap, window, 1.0,
+                           past=pasts[s]) for s, (lo, hi) in enumerate(zip(starts[:-1], starts[1:]))]
+    # alone, and with every sequence's keys shared among 2, 3 or more blocks than the shortest has tiles
+    for n_split in (1, 2, 3, 7) if dtype == "bfloat16" and not plain_kernel and new <= kernels.TALK_SPLIT_ROWS else (1,):
+        shared = {}
+        if n_split > 1:
+            shared = dict(n_split=n_split,
+                          parts=torch.full((n_seqs * n_split * H * new * (D + 2),), float("nan"), device=DEV))
+        out.zero_()
+        kernels.talking_attention(dev(q, DT[dtype]), out, ints(starts), ints(pasts), n_seqs=n_seqs, max_new=new, n_heads=H,
+                                  n_kv_heads=G, head_dim=D, scale=scale, window=window, cap=cap, temp=dev(temp),
+                                  slope=slopes(H), talk=dev(talk), k_pool=k_pool, v_pool=v_pool, table=ints(pages),
+                                  table_len=table_len, plain=plain_kernel, **shared)
+        got = out.double().cpu().numpy()
+        for s, (lo, hi) in enumerate(zip(starts[:-1], starts[1:])):
+            close(got[lo:hi], wants[s], TOL[dtype], f"{n_split} blocks, sequence {s}: ")
 
 
+def test_how_a_steps_keys_are_shared_among_blocks():
+    assert kernels.talking_attention_split(8, 17, 4, 32, 0, 4000) == (1, 0)
+    assert kernels.talking_attention_split(1000, 1, 4, 32, 0, 4000) == (1, 0)
+    n_split, need = kernels.talking_attention_split(8, 1, 4, 32, 100, 4000)
+    assert n_split == 5 and need == 8 * 5 * 4 * 1 * 34          # a window of 100 keys: 4 tiles, or 5 where it straddles
+    n_split, need = kernels.talking_attention_split(3, 2, 6, 24, 0, 100000)
+    assert n_split == 99 and need == 3 * 99 * 6 * 2 * 26
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("distance, seen", [(0, True), (1, True), (63, True), (64, True), (70, True), (71, False), (300, False)])
-def test_one_loud_key_at_and_past_the_windows_edge(distance, seen):
+def test_one_loud_key_at_and_past_the_windows_edge(dtype, distance, seen):
     """A window of 71: one key that every head's query prefers by far carries the row if it is at most 70 positions
     back, and is gone at 71; the values tell."""
     H, G, D, window, n = 4, 2, 16, 71, 400
@@ -217,16 +239,17 @@ def test_one_loud_key_at_and_past_the_windows_edge(distance, seen):
     q[-1] = 1.0
     k[at] = 3.0
     v[at] = 50.0
+    q, k, v = rounded(q, dtype), rounded(k, dtype), rounded(v, dtype)
     rows = np.concatenate([q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1)], axis=1)
-    t_rows = dev(rows)
-    out = torch.zeros((n, H * D), device=DEV)
+    t_rows = dev(rows, DT[dtype])
+    out = torch.zeros((n, H * D), dtype=DT[dtype], device=DEV)
     kernels.talking_attention(t_rows[:, :H * D], out, ints([0, n]), ints([0]), n_seqs=1, max_new=n, n_heads=H, n_kv_heads=G,
                               head_dim=D, scale=1.0, window=window, cap=200.0, slope=slopes(H), k=t_rows[:, H * D:(H + G) * D],
                               v=t_rows[:, (H + G) * D:])
-    last = out[-1].cpu().numpy()
-    assert (np.abs(last - 50.0).max() < 1e-2) if seen else (np.abs(last).max() < 10.0)
+    last = out[-1].double().cpu().numpy()
+    assert (np.abs(last - 50.0).max() < (1e-2 if dtype == "float32" else 0.3)) if seen else (np.abs(last).max() < 10.0)
     want = plain_talking(q, k, v, None, None, None, 1.0, 200.0, window, 1.0)
-    close(out.double().cpu().numpy(), want, 2e-5)
+    close(out.double().cpu().numpy(), want, TOL[dtype])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -267,6 +290,51 @@ def test_selective_scan_carries_its_state(dtype, inner, n_state, rank):
     for r, slot in enumerate(slots):
         close(state[slot].double().cpu().numpy(), S[r], 2e-5)
     assert float(state[1].abs().sum()) == 0 and float(state[2].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("inner, n_state, rank", [(40, 12, 5), (24, 70, 4), (130, 16, 8)])
+@pytest.mark.parametrize("lengths", [[200, 1, 70, 65], [64, 129, 2, 1000], [4200, 3, 128, 127]])
+def test_selective_scan_in_pieces_side_by_side(inner, n_state, rank, lengths):
+    """Long runs are cut into pieces that run side by side and are joined through each piece's end state; the result
+    and the stored state equal those of one walk over the run, from a state that is not zero."""
+    rng = np.random.default_rng(inner + n_state + lengths[0])
+    n_seqs = len(lengths)
+    slots = [int(v) for v in rng.permutation(n_seqs + 2)[:n_seqs]]
+    first = rng.standard_normal((n_seqs + 2, inner, n_state))
+    w_dt, b_dt = rng.standard_normal((inner, rank)) * rank ** -0.5, rng.standard_normal(inner) - 3.0
+    a_log, d_skip = rng.standard_normal((inner, n_state)) * 0.5 - 1.0, rng.standard_normal(inner)
+    starts, _ = step_tables(lengths)
+    total = starts[-1]
+    xz = rng.standard_normal((total, 2 * inner))
+    low = rng.standard_normal((total, rank + 2 * n_state))
+    t_xz, t_low = dev(xz), dev(low)
+    dt = torch.zeros((total, inner), device=DEV)
+    kernels.selective_scan_dt(t_low, dev(w_dt), dev(b_dt), dt, n_tokens=total)
+    results = []
+    for pieces in (False, True):
+        state = dev(first)
+        out = torch.zeros((total, inner), device=DEV)
+        extra = {}
+        if pieces:
+            piece, most, need = kernels.selective_scan_pieces(max(lengths), total, n_seqs, inner, n_state)
+            assert piece > 0 and need > 0 and most * piece >= max(lengths)
+            extra = dict(max_new=max(lengths), scratch=torch.full((need,), float("nan"), device=DEV))
+        kernels.selective_scan(t_xz[:, :inner], t_xz[:, inner:], dt, t_low, rank, rank + n_state, dev(a_log), dev(d_skip),
+                               state, ints(slots), ints(starts), out, n_seqs=n_seqs, **extra)
+        results.append((out.double().cpu().numpy(), state.double().cpu().numpy()))
+    close(results[1][0], results[0][0], 2e-5)
+    close(results[1][1], results[0][1], 2e-5)
+    # the pieces against the plain recurrence, on the second longest run
+    r = int(np.argsort(lengths)[-2])
+    lo, hi = starts[r], starts[r + 1]
+    t32 = lambda a: a.astype(np.float32).astype(np.float64)
+    S, A, dt64 = t32(first[slots[r]]), -np.exp(t32(a_log)), dt.double().cpu().numpy()
+    for t in range(lo, hi):
+        x, z = t32(xz[t, :inner]), t32(xz[t, inner:])
+        B, C = t32(low[t, rank:rank + n_state]), t32(low[t, rank + n_state:])
+        S = np.exp(dt64[t][:, None] * A) * S + (dt64[t] * x)[:, None] * B[None, :]
+        close(results[1][0][t], (S @ C + t32(d_skip) * x) * plain.silu(z), 5e-5, f"token {t - lo}: ")
+    close(results[1][1][slots[r]], S, 5e-5)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
