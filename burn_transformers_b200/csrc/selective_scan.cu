@@ -22,6 +22,7 @@ namespace bt {
 
 constexpr int SS_TT = 16;        // tokens staged at a time
 constexpr int SS_THREADS = 128;
+constexpr int SS_WS = 257;       // floats between the rank indices of the step sizes' weights in shared memory
 
 __device__ __forceinline__ float ss_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
@@ -32,30 +33,43 @@ selective_scan_dt_kernel(const T* __restrict__ low, long long low_row_stride, co
                          const float* __restrict__ b_dt, float* __restrict__ dt, long long n_tokens, int channels,
                          int rank) {
   extern __shared__ float sm[];
-  float* w_s = sm;                    // [rank][256]
-  float* low_s = w_s + rank * 256;    // [SS_TT][rank]
+  float* low_s = sm;                       // [rank][SS_TT]
+  float* w_s = low_s + rank * SS_TT;       // [rank][SS_WS]: padded, so that the transposing stores spread over the banks
   pdl_trigger();
   const int c0 = blockIdx.x * 256, c = c0 + threadIdx.x;
   for (int i = threadIdx.x; i < rank * 256; i += 256) {
     const int cl = i / rank, r = i - cl * rank;
-    w_s[r * 256 + cl] = c0 + cl < channels ? w_dt[(long long)(c0 + cl) * rank + r] : 0.f;
+    w_s[r * SS_WS + cl] = c0 + cl < channels ? w_dt[(long long)(c0 + cl) * rank + r] : 0.f;
   }
   const float bias = c < channels ? b_dt[c] : 0.f;
   pdl_wait();
   for (long long t0 = (long long)blockIdx.y * SS_TT; t0 < n_tokens; t0 += (long long)gridDim.y * SS_TT) {
     const int nt = (int)min((long long)SS_TT, n_tokens - t0);
     __syncthreads();
-    for (int i = threadIdx.x; i < nt * rank; i += 256) {
+    for (int i = threadIdx.x; i < SS_TT * rank; i += 256) {
       const int t = i / rank, r = i - t * rank;
-      low_s[i] = to_float(low[(t0 + t) * low_row_stride + r]);
+      low_s[r * SS_TT + t] = t < nt ? to_float(low[(t0 + t) * low_row_stride + r]) : 0.f;
     }
     __syncthreads();
-    if (c < channels) {
-      for (int t = 0; t < nt; ++t) {
-        float acc = bias;
-        for (int r = 0; r < rank; ++r) acc = fmaf(w_s[r * 256 + threadIdx.x], low_s[t * rank + r], acc);
-        dt[(t0 + t) * channels + c] = ss_softplus(acc);
+    // a thread a channel: its weight once per rank index against the SS_TT tokens' numbers, read four at a time
+    float acc[SS_TT];
+#pragma unroll
+    for (int t = 0; t < SS_TT; ++t) acc[t] = bias;
+    for (int r = 0; r < rank; ++r) {
+      const float w = w_s[r * SS_WS + threadIdx.x];
+#pragma unroll
+      for (int t4 = 0; t4 < SS_TT / 4; ++t4) {
+        const float4 x = *reinterpret_cast<const float4*>(low_s + r * SS_TT + t4 * 4);
+        acc[t4 * 4 + 0] = fmaf(w, x.x, acc[t4 * 4 + 0]);
+        acc[t4 * 4 + 1] = fmaf(w, x.y, acc[t4 * 4 + 1]);
+        acc[t4 * 4 + 2] = fmaf(w, x.z, acc[t4 * 4 + 2]);
+        acc[t4 * 4 + 3] = fmaf(w, x.w, acc[t4 * 4 + 3]);
       }
+    }
+    if (c < channels) {
+#pragma unroll
+      for (int t = 0; t < SS_TT; ++t)
+        if (t < nt) dt[(t0 + t) * channels + c] = ss_softplus(acc[t]);
     }
   }
 }
@@ -212,9 +226,10 @@ extern "C" int bt_selective_scan_dt(const void* low, long long low_row_stride, c
   BT_CHECK(channels > 0 && rank > 0 && rank <= 160 && n_tokens >= 0,
            "selective_scan_dt: bad sizes channels=%d rank=%d (at most 160)", channels, rank);
   if (n_tokens == 0) return 0;
-  const size_t smem = sizeof(float) * ((size_t)rank * 256 + (size_t)SS_TT * rank);
+  const size_t smem = sizeof(float) * ((size_t)rank * SS_WS + (size_t)SS_TT * rank);
   const long long tiles = (n_tokens + SS_TT - 1) / SS_TT;
-  const dim3 grid((channels + 255) / 256, (unsigned)(tiles < 4096 ? tiles : 4096));
+  const long long col_blocks = (channels + 255) / 256, want_rows = (4 * 148 + col_blocks - 1) / col_blocks;
+  const dim3 grid((unsigned)col_blocks, (unsigned)(tiles < want_rows ? tiles : want_rows));      // (about four blocks an SM)
 #define BT_SSD(T)                                                                                                     \
   do {                                                                                                                \
     auto kern = selective_scan_dt_kernel<T>;                                                                          \

@@ -5,8 +5,9 @@
 //
 // A block is 16 query tokens of one sequence with ALL heads, a warp a head.  Per tile of 32 keys: warp g multiplies its
 // head's queries with the tile's keys (mma.sync, 16 x 32 scores in the accumulators), caps and biases them and leaves
-// them in shared memory; after a barrier warp h sums the heads' planes with row h of `talk` in the accumulators' own
-// layout, so that the weights pass from there to the value product's operand inside registers.  Key and value tiles
+// them in shared memory, every lane its own accumulators as 16-byte pieces; after a barrier warp h sums the heads'
+// planes with row h of `talk`, lane by lane in the same layout, so that the weights pass from the accumulators to the
+// value product's operand inside registers.  Key and value tiles
 // (per key head, shared by its query heads) come through two cp.async buffers from the step's own rows or the pages.
 // A step that brings at most 16 tokens a sequence (a decode step is the same block with one live row) may be cut over
 // the keys: block b of `n_split` takes every n_split-th tile and leaves its running maximum, sum and accumulators in
@@ -15,7 +16,7 @@
 
 namespace bt {
 
-constexpr int TM_BQ = 16, TM_KT = 32, TM_PAD = 8, TM_RS = TM_KT + 8;
+constexpr int TM_BQ = 16, TM_KT = 32, TM_PAD = 8;
 
 struct TalkingArgs {
   const __nv_bfloat16 *q, *gate;
@@ -37,7 +38,7 @@ __device__ __forceinline__ void tm_cp_async16(unsigned dst, const void* src, int
 
 static size_t tm_smem(int H, int G, int dp) {
   return (size_t)2 * TM_BQ * (H * dp + TM_PAD) + (size_t)2 * 2 * 2 * G * TM_KT * (dp + TM_PAD) +
-         sizeof(float) * ((size_t)H * TM_BQ * TM_RS + (size_t)H * H);
+         sizeof(float) * ((size_t)H * TM_BQ * TM_KT + (size_t)H * H);
 }
 
 // NP: 16-channel pieces of a head (head_dim <= 16 NP); WB: the most warps of a block
@@ -51,8 +52,8 @@ __global__ void __launch_bounds__(32 * WB) talking_attention_mma_kernel(TalkingA
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(tm_raw);      // [16][ldq]
   __nv_bfloat16* k_s = q_s + TM_BQ * ldq;                             // [2][G][32][ldk]
   __nv_bfloat16* v_s = k_s + 2 * G * TM_KT * ldk;                     // [2][G][32][ldk]
-  float* r_s = reinterpret_cast<float*>(v_s + 2 * G * TM_KT * ldk);   // [H][16][TM_RS]
-  float* t_s = r_s + H * TM_BQ * TM_RS;                               // [H][H]
+  float* r_s = reinterpret_cast<float*>(v_s + 2 * G * TM_KT * ldk);   // [H][4][32 lanes][4]: a lane's own accumulators
+  float* t_s = r_s + H * TM_BQ * TM_KT;                               // [H][H]
   pdl_trigger();
   pdl_wait();
   const int seq = blockIdx.y;
@@ -72,7 +73,7 @@ __global__ void __launch_bounds__(32 * WB) talking_attention_mma_kernel(TalkingA
     if (r < nq && c < chunks) val = *reinterpret_cast<const uint4*>(p.q + (long long)(t0 + q0 + r) * p.q_row + h * D + c * 8);
     *reinterpret_cast<uint4*>(q_s + r * ldq + h * dp + c * 8) = val;
   }
-  for (int i = tid; i < H * H; i += n_threads) t_s[i] = p.talk ? p.talk[i] : (i / H == i % H ? 1.f : 0.f);
+  for (int i = tid; i < H * H; i += n_threads) t_s[i] = (p.talk ? p.talk[i] : (i / H == i % H ? 1.f : 0.f)) * LOG2E;
   // channels past head_dim of the key and value tiles, which no copy writes
   if (chunks < dchunks)
     for (int i = tid; i < 2 * 2 * G * TM_KT * (dchunks - chunks); i += n_threads) {
@@ -123,9 +124,9 @@ __global__ void __launch_bounds__(32 * WB) talking_attention_mma_kernel(TalkingA
   load_tile(tile_lo, 0);
   const float my_scale = p.scale * (p.temp ? p.temp[head] : 1.f);
   const float my_slope = p.slope ? p.slope[head] : 0.f;
-  const float inv_cap = p.cap > 0.f ? 1.f / p.cap : 0.f;
-  const int qpos0 = past + q0 + g, qpos1 = qpos0 + 8;
-  const bool live0 = g < nq, live1 = g + 8 < nq;
+  const float two_inv_cap = p.cap > 0.f ? 2.f / p.cap : 0.f;
+  const int qpos0 = past + q0 + g;                       // the lane's rows: this position and the one 8 further
+  const int seen_span = p.window > 0 ? p.window : 0x7fffffff;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float acc[2 * NP][4];
 #pragma unroll
@@ -138,7 +139,7 @@ __global__ void __launch_bounds__(32 * WB) talking_attention_mma_kernel(TalkingA
   // transposed (rows = keys, 8 channels a row)
   const unsigned k_lane = (unsigned)(((kv_head * TM_KT + (mi >> 1) * 8 + lr) * ldk + (mi & 1) * 8) * 2);
   const unsigned v_lane = (unsigned)(((kv_head * TM_KT + (mi & 1) * 8 + lr) * ldk + (mi >> 1) * 8) * 2);
-  float* r_mine = r_s + head * TM_BQ * TM_RS;
+  float* r_mine = r_s + head * (NT * 128);
 
   for (int tile = tile_lo, buf = 0; tile < tile_hi; tile += tile_step, buf ^= 1) {
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
@@ -163,51 +164,54 @@ __global__ void __launch_bounds__(32 * WB) talking_attention_mma_kernel(TalkingA
         ds_mma(s[2 * n2 + 1], a[0], a[1], a[2], a[3], b[2], b[3]);
       }
     }
-    // this head's raw scores: scale and temperature, the cap, the distance's bias
+    // this head's raw scores: scale and temperature, the cap, the distance's bias.  rel0: how far the lane's first key
+    // lies behind its first row; element (n, e) lies 8 (e >> 1) - 8 n - (e & 1) further
+    const int rel0 = qpos0 - key0 - qd * 2;
+    const float bias0 = my_slope * (float)rel0;
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         float x = s[n][e] * my_scale;
-        if (p.cap > 0.f) x = p.cap * (1.f - __fdividef(2.f, __expf(2.f * x * inv_cap) + 1.f));
-        const int kp = key0 + n * 8 + qd * 2 + (e & 1);
-        s[n][e] = x - my_slope * (float)((e < 2 ? qpos0 : qpos1) - kp);
+        if (p.cap > 0.f) x = p.cap * (1.f - __fdividef(2.f, __expf(x * two_inv_cap) + 1.f));
+        s[n][e] = x - fmaf(my_slope, (float)(8 * (e >> 1) - 8 * n - (e & 1)), bias0);
       }
-      *reinterpret_cast<float2*>(r_mine + g * TM_RS + n * 8 + qd * 2) = make_float2(s[n][0], s[n][1]);
-      *reinterpret_cast<float2*>(r_mine + (g + 8) * TM_RS + n * 8 + qd * 2) = make_float2(s[n][2], s[n][3]);
+      *reinterpret_cast<float4*>(r_mine + (n * 32 + lane) * 4) = make_float4(s[n][0], s[n][1], s[n][2], s[n][3]);
     }
     __syncthreads();
-    // the heads' planes summed with this head's row of `talk`
+    // the heads' planes summed with this head's row of `talk` (times log2 e: the softmax works in base 2)
 #pragma unroll
     for (int n = 0; n < NT; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
     for (int h2 = 0; h2 < H; ++h2) {
       const float w = t_s[head * H + h2];
-      const float* src = r_s + h2 * TM_BQ * TM_RS + qd * 2;
+      const float* src = r_s + h2 * (NT * 128) + lane * 4;
 #pragma unroll
       for (int n = 0; n < NT; ++n) {
-        const float2 lo = *reinterpret_cast<const float2*>(src + g * TM_RS + n * 8);
-        const float2 hi = *reinterpret_cast<const float2*>(src + (g + 8) * TM_RS + n * 8);
-        s[n][0] = fmaf(w, lo.x, s[n][0]);
-        s[n][1] = fmaf(w, lo.y, s[n][1]);
-        s[n][2] = fmaf(w, hi.x, s[n][2]);
-        s[n][3] = fmaf(w, hi.y, s[n][3]);
+        const float4 x = *reinterpret_cast<const float4*>(src + n * 128);
+        s[n][0] = fmaf(w, x.x, s[n][0]);
+        s[n][1] = fmaf(w, x.y, s[n][1]);
+        s[n][2] = fmaf(w, x.z, s[n][2]);
+        s[n][3] = fmaf(w, x.w, s[n][3]);
       }
+    }
+    // every key of the tile before every row of the block and inside its window: nothing to hide
+    const bool full = key0 + TM_KT - 1 <= pos_first && pos_first + TM_BQ - 1 - key0 < seen_span;
+    if (!full) {
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int rel = rel0 + 8 * (e >> 1) - 8 * n - (e & 1);
+          if ((unsigned)rel >= (unsigned)seen_span) s[n][e] = -INFINITY;
+        }
     }
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int n = 0; n < NT; ++n)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int kp = key0 + n * 8 + qd * 2 + (e & 1);
-        const int qp = e < 2 ? qpos0 : qpos1;
-        bool seen = (e < 2 ? live0 : live1) && kp <= qp;
-        if (p.window > 0) seen = seen && qp - kp < p.window;
-        const float v = seen ? s[n][e] * LOG2E : -INFINITY;
-        s[n][e] = v;
-        mx[e >> 1] = fmaxf(mx[e >> 1], v);
-      }
+      for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
     float corr[2];
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
@@ -217,6 +221,8 @@ __global__ void __launch_bounds__(32 * WB) talking_attention_mma_kernel(TalkingA
       corr[u] = m_new == -INFINITY ? 1.f : ds_exp2(m_run[u] - m_new);
       m_run[u] = m_new;
     }
+    // (a row that has seen no key yet keeps the maximum -inf; its weights are 2^(-inf - 0) = 0)
+    const float m_use[2] = {m_run[0] == -INFINITY ? 0.f : m_run[0], m_run[1] == -INFINITY ? 0.f : m_run[1]};
     float psum[2] = {0.f, 0.f};
     unsigned p_hi[NT][2], p_lo[NT][2];
 #pragma unroll
@@ -224,7 +230,7 @@ __global__ void __launch_bounds__(32 * WB) talking_attention_mma_kernel(TalkingA
       float w[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        w[e] = s[n][e] == -INFINITY ? 0.f : ds_exp2(s[n][e] - m_run[e >> 1]);
+        w[e] = ds_exp2(s[n][e] - m_use[e >> 1]);
         psum[e >> 1] += w[e];
       }
 #pragma unroll
