@@ -159,6 +159,26 @@ class SandwichBlock(Block):
     def graph_safe(self):
         return all(p.graph_safe for p in self.parts().values())
 
+    def _mixers_side_by_side(self, ctx, x, branch, entry, owns_cache):
+        """The two mixers of the layer need nothing of one another: the right one runs on a stream of its own and adds
+        into a zeroed buffer of its own, which one kernel then adds to the left one's (as ParallelBlock runs a layer's
+        parts; the same streams)."""
+        n = ctx.n_tokens
+        side, = ParallelBlock._sides(branch.device, 1)
+        held, ctx.ws.hold = ctx.ws.hold, True
+        step_side, ctx.side = getattr(ctx, "side", None), None
+        try:
+            other = ctx.ws.take((n, branch.shape[1]), torch.float32)
+            side.fork()
+            with side.stream_context():
+                other.zero_()
+                self.mixer.right.forward(ctx, x, other, entry, owns_cache)
+            self.mixer.left.forward(ctx, x, branch, entry, owns_cache)
+        finally:
+            side.join()
+            ctx.ws.hold, ctx.side = held, step_side
+        kernels.add_rows(branch, [other], n_rows=n)
+
     def forward(self, ctx, residual, entry, owns_cache=True):
         if getattr(ctx, "program", None) is not None:
             from ..engine.program import ProgramUnsupported
@@ -169,7 +189,10 @@ class SandwichBlock(Block):
         x = self.norm1.forward(ctx, residual, ctx.dtype, lazy=False)
         inner = ctx.ws.mark()
         branch.zero_()
-        self.mixer.forward(ctx, x, branch, entry, owns_cache)
+        if hasattr(self.mixer, "left") and n <= ParallelBlock.side_by_side_up_to and residual.device.type == "cuda":
+            self._mixers_side_by_side(ctx, x, branch, entry, owns_cache)
+        else:
+            self.mixer.forward(ctx, x, branch, entry, owns_cache)
         ctx.ws.release(inner)
         if self.feed_forward is None:
             kernels.rmsnorm_add(branch, self.norm1b.t_weight, residual, self.norm1b.eps, n_rows=n)
