@@ -26,6 +26,19 @@ constexpr int SS_WS = 257;       // floats between the rank indices of the step 
 
 __device__ __forceinline__ float ss_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
+// exp(d * a) for the decay of a step, a <= 0.  With bfloat16 rows the exponent is formed in base 2 (a_scaled = a log2 e)
+// and raised by the special-function unit (2 units in the last place); 32-bit rows take the library's exp.
+template <typename T>
+__device__ __forceinline__ float ss_decay(float d, float a_scaled) {
+  if constexpr (sizeof(T) == 2) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(d * a_scaled));
+    return y;
+  } else {
+    return expf(d * a_scaled);
+  }
+}
+
 // dt[t, c], a block: 256 channels x SS_TT tokens; W_dt's rows of these channels lie transposed in shared memory
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -93,9 +106,11 @@ selective_scan_kernel(const T* __restrict__ x, long long x_row_stride, const T* 
   const int c = blockIdx.x * CPB + c_local;
   const bool owns = c < channels;
   const int n0 = part * NS;
-  float a[NS], s[NS];
+  float a[NS], s[NS];      // a: A = -exp(A_log), times log2 e where the decays are raised in base 2
 #pragma unroll
-  for (int i = 0; i < NS; ++i) a[i] = owns && n0 + i < n_state ? -expf(a_log[(long long)c * n_state + n0 + i]) : 0.f;
+  for (int i = 0; i < NS; ++i)
+    a[i] = owns && n0 + i < n_state ? -expf(a_log[(long long)c * n_state + n0 + i]) * (sizeof(T) == 2 ? 1.4426950408889634f : 1.f)
+                                    : 0.f;
   const float skip = owns ? d_skip[c] : 0.f;
   pdl_wait();
   const int first = seq_start[seq], n_all = seq_start[seq + 1] - first;
@@ -117,7 +132,7 @@ selective_scan_kernel(const T* __restrict__ x, long long x_row_stride, const T* 
       const float d = e[n_state];
 #pragma unroll
       for (int i = 0; i < NS; ++i)
-        if (n0 + i < n_state) s[i] = fmaf(expf(d * a[i]), s[i], e[n0 + i]);
+        if (n0 + i < n_state) s[i] = fmaf(ss_decay<T>(d, a[i]), s[i], e[n0 + i]);
     }
   }
   for (int t0 = t_lo; t0 < t_hi; t0 += SS_TT) {
@@ -146,7 +161,7 @@ selective_scan_kernel(const T* __restrict__ x, long long x_row_stride, const T* 
 #pragma unroll
       for (int i = 0; i < NS; ++i) {
         if (n0 + i < n_state) {
-          s[i] = fmaf(expf(d * a[i]), s[i], dx * bt_[i]);
+          s[i] = fmaf(ss_decay<T>(d, a[i]), s[i], dx * bt_[i]);
           y = fmaf(s[i], ct_[i], y);
         }
       }
