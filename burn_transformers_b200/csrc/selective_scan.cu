@@ -94,13 +94,13 @@ selective_scan_kernel(const T* __restrict__ x, long long x_row_stride, const T* 
                       int c_off, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                       float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ seq_start,
                       T* __restrict__ out, long long out_row_stride, int channels, int n_state, float out_scale, int piece,
-                      float* __restrict__ ends) {
+                      float* __restrict__ ends, int stage) {
   constexpr int CPB = SS_THREADS / LANES;      // channels per block
   extern __shared__ float sm[];
-  float* bc_s = sm;                            // [SS_TT][2 * n_state]
-  float* dt_s = bc_s + SS_TT * 2 * n_state;    // [SS_TT][CPB]
-  float* x_s = dt_s + SS_TT * CPB;
-  float* z_s = x_s + SS_TT * CPB;
+  float* bc_s = sm;                            // [stage][2 * n_state]
+  float* dt_s = bc_s + stage * 2 * n_state;    // [stage][CPB]
+  float* x_s = dt_s + stage * CPB;
+  float* z_s = x_s + stage * CPB;
   pdl_trigger();
   const int seq = blockIdx.y, c_local = threadIdx.x / LANES, part = threadIdx.x % LANES;
   const int c = blockIdx.x * CPB + c_local;
@@ -135,8 +135,10 @@ selective_scan_kernel(const T* __restrict__ x, long long x_row_stride, const T* 
         if (n0 + i < n_state) s[i] = fmaf(ss_decay<T>(d, a[i]), s[i], e[n0 + i]);
     }
   }
-  for (int t0 = t_lo; t0 < t_hi; t0 += SS_TT) {
-    const int nt = min(SS_TT, t_hi - t0);
+  // B and C of a token as 16-byte pieces where the lane's state indices are whole pieces of a row
+  const bool vec = (n_state & 3) == 0 && n0 + NS <= n_state;
+  for (int t0 = t_lo; t0 < t_hi; t0 += stage) {
+    const int nt = min(stage, t_hi - t0);
     __syncthreads();
     for (int i = threadIdx.x; i < nt * 2 * n_state; i += SS_THREADS) {
       const int t = i / (2 * n_state), n = i - t * 2 * n_state;
@@ -158,11 +160,25 @@ selective_scan_kernel(const T* __restrict__ x, long long x_row_stride, const T* 
       const float* bt_ = bc_s + t * 2 * n_state + n0;
       const float* ct_ = bt_ + n_state;
       float y = 0.f;
+      if (vec) {
 #pragma unroll
-      for (int i = 0; i < NS; ++i) {
-        if (n0 + i < n_state) {
-          s[i] = fmaf(ss_decay<T>(d, a[i]), s[i], dx * bt_[i]);
-          y = fmaf(s[i], ct_[i], y);
+        for (int i4 = 0; i4 < NS / 4; ++i4) {
+          const float4 b4 = *reinterpret_cast<const float4*>(bt_ + 4 * i4), c4 = *reinterpret_cast<const float4*>(ct_ + 4 * i4);
+          const float bs[4] = {b4.x, b4.y, b4.z, b4.w}, cs[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int i = 4 * i4 + k;
+            s[i] = fmaf(ss_decay<T>(d, a[i]), s[i], dx * bs[k]);
+            y = fmaf(s[i], cs[k], y);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < NS; ++i) {
+          if (n0 + i < n_state) {
+            s[i] = fmaf(ss_decay<T>(d, a[i]), s[i], dx * bt_[i]);
+            y = fmaf(s[i], ct_[i], y);
+          }
         }
       }
       if (!ENDS) {
@@ -211,16 +227,24 @@ static int launch_selective_scan(const T* x, long long xs, const T* z, long long
   BT_CHECK(n_state <= 512, "selective_scan: %d state indices a channel; the kernel takes up to 512", n_state);
   const int cpb = SS_THREADS / lanes;
   const dim3 grid((channels + cpb - 1) / cpb, n_seqs, piece > 0 ? max_pieces : 1);
-  const size_t smem = sizeof(float) * ((size_t)SS_TT * 2 * n_state + 3 * (size_t)SS_TT * cpb);
+  const int stage = n_state <= 64 ? 2 * SS_TT : SS_TT;      // tokens staged in shared memory at a time
+  const size_t smem = sizeof(float) * ((size_t)stage * 2 * n_state + 3 * (size_t)stage * cpb);
 #define BT_SS(NS, LANES)                                                                                              \
   do {                                                                                                                \
+    if (smem > 48 * 1024)                                                                                             \
+      BT_CHECK(cudaFuncSetAttribute(selective_scan_kernel<T, NS, LANES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                    (int)smem) == cudaSuccess &&                                                      \
+               cudaFuncSetAttribute(selective_scan_kernel<T, NS, LANES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                    (int)smem) == cudaSuccess, "selective_scan: cannot reserve %zu bytes of shared memory", smem); \
     if (piece > 0)                                                                                                    \
       BT_PDL_OK("selective_scan", launch_pdl(selective_scan_kernel<T, NS, LANES, true>, grid, dim3(SS_THREADS), smem, \
                                              stream, 1, x, xs, z, zs, dt, low, ls, b_off, c_off, a_log, d_skip, state, \
-                                             slots, seq_start, out, os, channels, n_state, out_scale, piece, ends));   \
+                                             slots, seq_start, out, os, channels, n_state, out_scale, piece, ends,     \
+                                             stage));                                                                 \
     BT_PDL_OK("selective_scan", launch_pdl(selective_scan_kernel<T, NS, LANES, false>, grid, dim3(SS_THREADS), smem,   \
                                            stream, 1, x, xs, z, zs, dt, low, ls, b_off, c_off, a_log, d_skip, state,   \
-                                           slots, seq_start, out, os, channels, n_state, out_scale, piece, ends));     \
+                                           slots, seq_start, out, os, channels, n_state, out_scale, piece, ends,       \
+                                           stage));                                                                   \
   } while (0)
   if (ns == 4) BT_SS(4, 4);
   else if (ns == 8) BT_SS(8, 4);

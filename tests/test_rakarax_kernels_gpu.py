@@ -254,7 +254,7 @@ def test_one_loud_key_at_and_past_the_windows_edge(dtype, distance, seen):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("inner, n_state, rank", [(80, 12, 5), (36, 5, 3), (30, 1, 2), (24, 70, 4), (16, 130, 6), (256, 32, 16),
-                                                  (20, 300, 160)])
+                                                  (20, 300, 160), (6, 512, 3), (64, 16, 4), (40, 64, 8)])
 def test_selective_scan_carries_its_state(dtype, inner, n_state, rank):
     rng = np.random.default_rng(inner + n_state)
     slots = [3, 0, 4]
