@@ -27,7 +27,7 @@ bool latent_attention_mma_supports(int rank, int rot);
 int launch_latent_attention_mma(const __nv_bfloat16* q, long long q_row_stride, const __nv_bfloat16* pool, const int* table,
                                 int table_stride, int table_len, int page_size, const int* seq_start, const int* past_len,
                                 const float* sink, __nv_bfloat16* out, long long out_row_stride, float* part, int n_seqs,
-                                int max_new, int n_heads, int rank, int rot, float scale, int n_splits,
+                                int max_new, int n_heads, int rank, int rot, float scale, int n_splits, int window,
                                 cudaStream_t stream);
 
 // per-head products on tensor cores for bfloat16 (head_linear_mma.cu)
@@ -153,7 +153,7 @@ latent_attention_kernel(const T* __restrict__ q, long long q_row_stride, const T
                         const int* __restrict__ seq_start, const int* __restrict__ past_len,
                         const float* __restrict__ sink, T* __restrict__ out, long long out_row_stride,
                         float* __restrict__ part, int n_heads, int hb, int tq, int head_tiles, int rank, int rot,
-                        float scale, int n_splits) {
+                        float scale, int n_splits, int window) {
   extern __shared__ float smem[];
   const int dk = rank + rot;
   const int ks = dk + 1;                       // key rows one float apart from a multiple of the banks
@@ -192,11 +192,13 @@ latent_attention_kernel(const T* __restrict__ q, long long q_row_stride, const T
 #pragma unroll
     for (int j = 0; j < DVL; ++j) acc[i][j] = 0.f;
   }
-  // keys this block may need: up to the position of its last token; cut into equal runs of tiles per split
+  // keys this block may need: from the first one its first token sees (`window` > 0: a row sees the last `window`
+  // positions up to its own) to the position of its last token; cut into equal runs of tiles per split
   const int last_pos = past + min(t0 + tq, n_new) - 1;
   const int n_tiles = last_pos / LA_TK + 1;
-  const int per = (n_tiles + n_splits - 1) / n_splits;
-  const int tile_lo = split * per, tile_hi = min(n_tiles, tile_lo + per);
+  const int tile_first = window > 0 ? max(0, past + t0 - window + 1) / LA_TK : 0;
+  const int per = (n_tiles - tile_first + n_splits - 1) / n_splits;
+  const int tile_lo = tile_first + split * per, tile_hi = min(n_tiles, tile_lo + per);
   for (int tile = tile_lo; tile < tile_hi; ++tile) {
     const int j0 = tile * LA_TK;
     __syncthreads();  // the previous tile's readers are done (and q_s is complete before the first use)
@@ -225,7 +227,7 @@ latent_attention_kernel(const T* __restrict__ q, long long q_row_stride, const T
     float p[RW];
 #pragma unroll
     for (int i = 0; i < RW; ++i) {
-      const bool seen = row_ok[i] && j0 + lane <= row_pos[i];
+      const bool seen = row_ok[i] && j0 + lane <= row_pos[i] && (window <= 0 || row_pos[i] - (j0 + lane) < window);
       const float sc = seen ? s[i] * scale : -INFINITY;
       const float m_new = fmaxf(m_run[i], warp_max(sc));
       const float corr = m_new == -INFINITY ? 1.f : expf(m_run[i] - m_new);
@@ -333,7 +335,7 @@ static int launch_latent_attention(const T* q, long long q_row_stride, const T* 
                                    int table_len, int page_size, const int* seq_start, const int* past_len,
                                    const float* sink, T* out, long long out_row_stride, float* part, int n_tokens,
                                    int n_seqs, int max_new, int n_heads, int rank, int rot, float scale, int n_splits,
-                                   cudaStream_t stream) {
+                                   int window, cudaStream_t stream) {
   const int dk = rank + rot;
   const int dvl = (rank + 31) / 32;
   int rw, dvl_t;
@@ -359,7 +361,7 @@ static int launch_latent_attention(const T* q, long long q_row_stride, const T* 
     BT_PDL_OK("latent_attention",                                                                                    \
               launch_pdl(kernel, grid, block, smem, stream, 1, q, q_row_stride, pool, table, table_stride, table_len, \
                          page_size, seq_start, past_len, sink, out, out_row_stride, part, n_heads, hb, tq, head_tiles, \
-                         rank, rot, scale, n_splits));                                                               \
+                         rank, rot, scale, n_splits, window));                                                       \
   } while (0)
   if (rw == 4 && dvl_t == 2) BT_LA(4, 2);
   else if (rw == 4 && dvl_t == 4) BT_LA(4, 4);
@@ -480,11 +482,12 @@ extern "C" int bt_latent_attention(const void* q, long long q_row_stride, const 
                                    int table_stride, int table_len, int page_size, const int* seq_start,
                                    const int* past_len, const float* sink, void* out, long long out_row_stride,
                                    float* part, int n_tokens, int n_seqs, int max_new, int n_heads, int rank, int rot,
-                                   float scale, int n_splits, int tensor_cores, int merge, int dtype,
+                                   float scale, int n_splits, int window, int tensor_cores, int merge, int dtype,
                                    cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_heads > 0 && rank > 0 && rot >= 0 && rank <= 512, "latent_attention: bad sizes heads=%d rank=%d rot=%d (rank "
            "at most 512)", n_heads, rank, rot);
+  BT_CHECK(window >= 0, "latent_attention: a window of %d positions", window);
   BT_CHECK(n_splits >= 1 && n_splits <= LA_MAX_SPLITS && (n_splits == 1 || part != nullptr),
            "latent_attention: %d splits need scratch for their partial results", n_splits);
   BT_CHECK(table_len > 0 && page_size > 0 && n_seqs <= 65535, "latent_attention: bad table_len %d, page_size %d or %d "
@@ -494,7 +497,7 @@ extern "C" int bt_latent_attention(const void* q, long long q_row_stride, const 
     if (int e = launch_latent_attention<float>((const float*)q, q_row_stride, (const float*)pool, table, table_stride,
                                                table_len, page_size, seq_start, past_len, sink, (float*)out,
                                                out_row_stride, part, n_tokens, n_seqs, max_new, n_heads, rank, rot, scale,
-                                               n_splits, stream))
+                                               n_splits, window, stream))
       return e;
     if (!merge) return 0;
     return launch_latent_merge<float>(part, (float*)out, out_row_stride, n_tokens, n_heads, rank, n_splits, stream);
@@ -504,12 +507,13 @@ extern "C" int bt_latent_attention(const void* q, long long q_row_stride, const 
     if (tensor_cores && latent_attention_mma_supports(rank, rot))
       e = launch_latent_attention_mma((const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)pool, table,
                                       table_stride, table_len, page_size, seq_start, past_len, sink, (__nv_bfloat16*)out,
-                                      out_row_stride, part, n_seqs, max_new, n_heads, rank, rot, scale, n_splits, stream);
+                                      out_row_stride, part, n_seqs, max_new, n_heads, rank, rot, scale, n_splits, window,
+                                      stream);
     else
       e = launch_latent_attention<__nv_bfloat16>((const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)pool, table,
                                                  table_stride, table_len, page_size, seq_start, past_len, sink,
                                                  (__nv_bfloat16*)out, out_row_stride, part, n_tokens, n_seqs, max_new,
-                                                 n_heads, rank, rot, scale, n_splits, stream);
+                                                 n_heads, rank, rot, scale, n_splits, window, stream);
     if (e || !merge) return e;
     return launch_latent_merge<__nv_bfloat16>(part, (__nv_bfloat16*)out, out_row_stride, n_tokens, n_heads, rank,
                                               n_splits, stream);

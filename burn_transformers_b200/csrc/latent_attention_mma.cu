@@ -35,7 +35,8 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_row
                             int table_len, int page_size, const int* __restrict__ seq_start,
                             const int* __restrict__ past_len, const float* __restrict__ sink,
                             __nv_bfloat16* __restrict__ out, long long out_row_stride, float* __restrict__ part,
-                            int n_heads, int hb, int tq, int head_tiles, int rank, int rot, float scale, int n_splits) {
+                            int n_heads, int hb, int tq, int head_tiles, int rank, int rot, float scale, int n_splits,
+                            int window) {
   extern __shared__ __align__(16) unsigned char lm_smem[];
   constexpr int NT = LM_KT / VW / 8;        // 8-key score tiles per warp
   constexpr int NP = VCT / 16;              // pairs of 8-channel value tiles per warp
@@ -97,8 +98,10 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_row
   const float scale_log2 = scale * LOG2E;
   const int last_pos = past + min(t0 + tq, n_new) - 1;
   const int n_tiles = last_pos / LM_KT + 1;
-  const int per = (n_tiles + n_splits - 1) / n_splits;
-  const int tile_lo = split * per, tile_hi = min(n_tiles, tile_lo + per);
+  // (`window` > 0: a row sees the last `window` positions up to its own; tiles before the first token's are skipped)
+  const int tile_first = window > 0 ? max(0, past + t0 - window + 1) / LM_KT : 0;
+  const int per = (n_tiles - tile_first + n_splits - 1) / n_splits;
+  const int tile_lo = tile_first + split * per, tile_hi = min(n_tiles, tile_lo + per);
   const int row_chunks = dk / 8;
   auto load_tile = [&](int tile, int buf) {
     const int j0 = tile * LM_KT;
@@ -155,7 +158,8 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_row
         for (int e = 0; e < 4; ++e) {
           const int j = j0 + key_base + n * 8 + qd * 2 + (e & 1);
           const int rr = e >> 1;
-          const float v = (row_ok[rr] && j <= row_pos[rr]) ? s[n][e] * scale_log2 : -INFINITY;
+          const float v = (row_ok[rr] && j <= row_pos[rr] && (window <= 0 || row_pos[rr] - j < window))
+                              ? s[n][e] * scale_log2 : -INFINITY;
           s[n][e] = v;
           mx[rr] = fmaxf(mx[rr], v);
         }
@@ -285,7 +289,7 @@ bool latent_attention_mma_supports(int rank, int rot) { return lm_value_warps(ra
 int launch_latent_attention_mma(const __nv_bfloat16* q, long long q_row_stride, const __nv_bfloat16* pool, const int* table,
                                 int table_stride, int table_len, int page_size, const int* seq_start, const int* past_len,
                                 const float* sink, __nv_bfloat16* out, long long out_row_stride, float* part, int n_seqs,
-                                int max_new, int n_heads, int rank, int rot, float scale, int n_splits,
+                                int max_new, int n_heads, int rank, int rot, float scale, int n_splits, int window,
                                 cudaStream_t stream) {
   const int vw = lm_value_warps(rank, rot);
   BT_CHECK(vw != 0, "latent_attention: rank %d, rot %d is no shape of the tensor-core kernel", rank, rot);
@@ -312,7 +316,7 @@ int launch_latent_attention_mma(const __nv_bfloat16* q, long long q_row_stride, 
     BT_PDL_OK("latent_attention_mma",                                                                                \
               launch_pdl(kernel, grid, block, smem, stream, 1, q, q_row_stride, pool, table, table_stride, table_len, \
                          page_size, seq_start, past_len, sink, out, out_row_stride, part, n_heads, hb, tq, head_tiles, \
-                         rank, rot, scale, n_splits));                                                               \
+                         rank, rot, scale, n_splits, window));                                                       \
   } while (0)
   if (vw == 1 && vc <= 32) BT_LM(1, 32);
   else if (vw == 1 && vc <= 64) BT_LM(1, 64);

@@ -4,12 +4,16 @@
 //   moe_route    per token: z = W_r x in 32-bit, s = sigmoid(z); experts lie in `n_groups` equal groups of neighbours, a
 //                group's score is the sum of its two largest s, only the `keep` best groups may give experts; the `top`
 //                largest s among those are chosen (equal scores: the lower index); weights s / (sum of the chosen + 1e-20)
-//                * scale.
+//                * scale.  With `softmax` the scores are softmax(z) over all experts instead; `choice_bias` [E] is added
+//                to the scores for the choice only; without `normalise` the weights are the chosen scores as they are.
 //   moe_sort     counts the pairs per expert, gives each pair a row in expert order, and numbers the row tiles
 //                (tiles never straddle two experts).
-//   moe_expert_in   hidden[r] = pair rule(gate_e x, up_e x) for the rows of expert e (x gathered by the pair's token)
+//   moe_expert_in   hidden[r] = pair rule(gate_e x, up_e x) for the rows of expert e (x gathered by the pair's token), or,
+//                   for experts without a gate, act(up_e x)
 //   moe_expert_out  part[r] = weight(r) * down_e hidden[r]   (32-bit)
-//   moe_combine  stream[t] += sum over the token's pairs, in the order of its choices: no atomics, a fixed order.
+//   moe_combine  stream[t] += sum over the token's pairs, in the order of its choices: no atomics, a fixed order.  A pair
+//                whose expert's number is `n_stored` or more names an expert without tensors that hands its input on: the
+//                pair adds weight * input[t].
 //
 // The products exist as 32-bit multiply-adds (float32, and every shape), on tensor cores (bfloat16, mma.sync m16n8k16
 // with 32-bit accumulators, K a multiple of 8) and, for steps with few rows an expert, as a kernel that streams every
@@ -63,11 +67,12 @@ __device__ __forceinline__ void unpack_piece(const uint4& v, float (&o)[8]) {
 template <typename T, int NP>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ x, long long x_row_stride, const T* __restrict__ router, int n_tokens, int K, int E,
-                 int top, int n_groups, int keep, float scale, int* __restrict__ ids, float* __restrict__ weights) {
+                 int top, int n_groups, int keep, float scale, int softmax, const float* __restrict__ choice_bias,
+                 int normalise, int* __restrict__ ids, float* __restrict__ weights) {
   extern __shared__ float sm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* score = sm + (size_t)warp * 3 * E;   // [E] sigmoid scores
-  float* cand = score + E;                    // [E] scores still to choose from (-1: not allowed, -2: taken)
+  float* cand = score + E;                    // [E] scores still to choose from (-inf: not allowed, or taken)
   float* group = cand + E;                    // [n_groups] group scores
   pdl_trigger();
   pdl_wait();
@@ -105,7 +110,7 @@ moe_route_kernel(const T* __restrict__ x, long long x_row_stride, const T* __res
           for (int u = 0; u < V; ++u) acc = fmaf(xv[i][u], wv[u], acc);
         }
         acc = warp_sum(acc);
-        if (lane == 0 && e0 + j < E) score[e0 + j] = 1.f / (1.f + expf(-acc));
+        if (lane == 0 && e0 + j < E) score[e0 + j] = softmax ? acc : 1.f / (1.f + expf(-acc));
       }
     }
   } else {
@@ -120,12 +125,22 @@ moe_route_kernel(const T* __restrict__ x, long long x_row_stride, const T* __res
 #pragma unroll
       for (int j = 0; j < EB; ++j) {
         const float z = warp_sum(acc[j]);
-        if (lane == 0 && e0 + j < E) score[e0 + j] = 1.f / (1.f + expf(-z));
+        if (lane == 0 && e0 + j < E) score[e0 + j] = softmax ? z : 1.f / (1.f + expf(-z));
       }
     }
   }
   __syncwarp();
-  for (int e = lane; e < E; e += 32) cand[e] = score[e];
+  if (softmax) {
+    float top_z = -INFINITY;
+    for (int e = lane; e < E; e += 32) top_z = fmaxf(top_z, score[e]);
+    top_z = warp_max(top_z);
+    float denom = 0.f;
+    for (int e = lane; e < E; e += 32) denom += expf(score[e] - top_z);
+    denom = warp_sum(denom);
+    for (int e = lane; e < E; e += 32) score[e] = expf(score[e] - top_z) / denom;
+    __syncwarp();
+  }
+  for (int e = lane; e < E; e += 32) cand[e] = score[e] + (choice_bias != nullptr ? choice_bias[e] : 0.f);
   if (keep < n_groups) {
     const int size = E / n_groups;
     for (int g = lane; g < n_groups; g += 32) {
@@ -149,7 +164,7 @@ moe_route_kernel(const T* __restrict__ x, long long x_row_stride, const T* __res
       __syncwarp();
     }
     for (int e = lane; e < E; e += 32)
-      if (group[e / size] != -INFINITY) cand[e] = -1.f;
+      if (group[e / size] != -INFINITY) cand[e] = -INFINITY;
   }
   __syncwarp();
   float sum = 0.f;
@@ -160,15 +175,16 @@ moe_route_kernel(const T* __restrict__ x, long long x_row_stride, const T* __res
       if (cand[e] > v) { v = cand[e]; i = e; }
     warp_argmax(v, i);
     __syncwarp();
+    v = score[i];       // (the weight is the score itself, whatever was added for the choice)
     if (lane == 0) {
-      cand[i] = -2.f;
+      cand[i] = -INFINITY;
       ids[(long long)t * top + r] = i;
       weights[(long long)t * top + r] = v;
     }
     sum += v;
     __syncwarp();
   }
-  if (lane < top) {
+  if (normalise && lane < top) {
     const long long at = (long long)t * top + lane;
     weights[at] = weights[at] / (sum + 1e-20f) * scale;
   }
@@ -246,13 +262,16 @@ struct MoeArgs {
   long long a_row_stride;
 };
 
-// IN: hidden[r, j] = pair(gate_e[j] . x, up_e[j] . x), w: [E][2N][K];  else part[r, c] = weight * (down_e[c] . hidden[r]),
-// w: [E][N][K].
-template <typename T, bool IN>
+// MODE 1: hidden[r, j] = pair(gate_e[j] . x, up_e[j] . x), w: [E][2N][K];  MODE 2 (experts without a gate): hidden[r, j] =
+// act(up_e[j] . x), w: [E][N][K];  MODE 0: part[r, c] = weight * (down_e[c] . hidden[r]), w: [E][N][K].
+constexpr int kMoeOut = 0, kMoeInPair = 1, kMoeInPlain = 2;
+
+template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_expert_simt_kernel(const T* __restrict__ a, const T* __restrict__ w, void* __restrict__ out, MoeArgs p) {
+  constexpr bool IN = MODE != kMoeOut, PAIR = MODE == kMoeInPair;
   __shared__ float a_s[MS_BK][MS_BM + 1];
-  __shared__ float w_s[IN ? 2 : 1][MS_BK][MS_BN + 1];
+  __shared__ float w_s[PAIR ? 2 : 1][MS_BK][MS_BN + 1];
   __shared__ int src_row[MS_BM];
   pdl_trigger();
   pdl_wait();
@@ -265,8 +284,8 @@ moe_expert_simt_kernel(const T* __restrict__ a, const T* __restrict__ w, void* _
   }
   __syncthreads();
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // 4 columns, 2 rows a thread
-  float acc[IN ? 2 : 1][2][4] = {};
-  const T* w_e = w + (long long)expert * (IN ? 2 : 1) * p.N * p.K;
+  float acc[PAIR ? 2 : 1][2][4] = {};
+  const T* w_e = w + (long long)expert * (PAIR ? 2 : 1) * p.N * p.K;
   for (int k0 = 0; k0 < p.K; k0 += MS_BK) {
     for (int i = threadIdx.x; i < MS_BM * MS_BK; i += 256) {
       const int r = i / MS_BK, k = i - r * MS_BK;
@@ -277,14 +296,14 @@ moe_expert_simt_kernel(const T* __restrict__ a, const T* __restrict__ w, void* _
       const int n = i / MS_BK, k = i - n * MS_BK;
       const bool in = n0 + n < p.N && k0 + k < p.K;
       w_s[0][k][n] = in ? to_float(w_e[(long long)(n0 + n) * p.K + k0 + k]) : 0.f;
-      if (IN) w_s[1][k][n] = in ? to_float(w_e[(long long)(p.N + n0 + n) * p.K + k0 + k]) : 0.f;
+      if (PAIR) w_s[PAIR ? 1 : 0][k][n] = in ? to_float(w_e[(long long)(p.N + n0 + n) * p.K + k0 + k]) : 0.f;
     }
     __syncthreads();
 #pragma unroll 8
     for (int k = 0; k < MS_BK; ++k) {
       const float a0 = a_s[k][ty * 2], a1 = a_s[k][ty * 2 + 1];
 #pragma unroll
-      for (int h = 0; h < (IN ? 2 : 1); ++h)
+      for (int h = 0; h < (PAIR ? 2 : 1); ++h)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const float b = w_s[h][k][tx * 4 + c];
@@ -304,7 +323,8 @@ moe_expert_simt_kernel(const T* __restrict__ a, const T* __restrict__ w, void* _
       const int n = n0 + tx * 4 + c;
       if (n >= p.N) continue;
       if (IN)
-        reinterpret_cast<T*>(out)[r * p.N + n] = from_float<T>(gated_pair(acc[0][i][c], acc[IN ? 1 : 0][i][c], p.act, p.limit));
+        reinterpret_cast<T*>(out)[r * p.N + n] = from_float<T>(
+            PAIR ? gated_pair(acc[0][i][c], acc[PAIR ? 1 : 0][i][c], p.act, p.limit) : apply_activation(acc[0][i][c], p.act));
       else
         reinterpret_cast<float*>(out)[r * p.N + n] = acc[0][i][c] * p.pair_weight[p.order[r]];
     }
@@ -330,11 +350,12 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-template <bool IN>
+template <int MODE>
 __global__ void __launch_bounds__(128)
 moe_expert_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
                       MoeArgs p) {
-  constexpr int HALVES = IN ? 2 : 1;
+  constexpr bool IN = MODE != kMoeOut, PAIR = MODE == kMoeInPair;
+  constexpr int HALVES = PAIR ? 2 : 1;
   __shared__ __align__(16) __nv_bfloat16 a_s[MM_STAGES][MM_BM][MM_LD];
   __shared__ __align__(16) __nv_bfloat16 w_s[MM_STAGES][HALVES][MM_BN][MM_LD];
   __shared__ int src_row[MM_BM];
@@ -422,7 +443,8 @@ moe_expert_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* 
           const float v = acc[0][mt][nt][half * 2 + c];
           if (IN)
             reinterpret_cast<__nv_bfloat16*>(out)[r * p.N + n] =
-                __float2bfloat16_rn(gated_pair(v, acc[IN ? 1 : 0][mt][nt][half * 2 + c], p.act, p.limit));
+                __float2bfloat16_rn(PAIR ? gated_pair(v, acc[PAIR ? 1 : 0][mt][nt][half * 2 + c], p.act, p.limit)
+                                         : apply_activation(v, p.act));
           else
             reinterpret_cast<float*>(out)[r * p.N + n] = v * scale;
         }
@@ -436,10 +458,11 @@ moe_expert_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* 
 // byte is read by one warp; a block whose expert got no row ends at once.
 constexpr int MF_ROWS = 8, MF_COLS = 8, MF_KC = 2048;
 
-template <bool IN>
+template <int MODE>
 __global__ void __launch_bounds__(128)
 moe_expert_few_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
                       MoeArgs p) {
+  constexpr bool IN = MODE != kMoeOut, PAIR = MODE == kMoeInPair;
   __shared__ __align__(16) __nv_bfloat16 x_s[MF_ROWS][MF_KC];
   pdl_trigger();
   pdl_wait();
@@ -448,10 +471,10 @@ moe_expert_few_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* 
   if (count == 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * MF_COLS + warp * 2;
-  const __nv_bfloat16* w_e = w + (long long)expert * (IN ? 2 : 1) * p.N * p.K;
+  const __nv_bfloat16* w_e = w + (long long)expert * (PAIR ? 2 : 1) * p.N * p.K;
   for (int r0 = 0; r0 < count; r0 += MF_ROWS) {
     const int rows = min(MF_ROWS, count - r0);
-    float acc[IN ? 2 : 1][2][MF_ROWS] = {};
+    float acc[PAIR ? 2 : 1][2][MF_ROWS] = {};
     for (int k0 = 0; k0 < p.K; k0 += MF_KC) {
       const int kc = min(MF_KC, p.K - k0);
       __syncthreads();
@@ -470,9 +493,9 @@ moe_expert_few_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* 
         const int n = n0 + col;
         if (n >= p.N) continue;
         for (int k = lane * 8; k < kc; k += 256) {
-          float wv[IN ? 2 : 1][8];
+          float wv[PAIR ? 2 : 1][8];
           load_piece(w_e + (long long)n * p.K + k0 + k, wv[0]);
-          if (IN) load_piece(w_e + (long long)(p.N + n) * p.K + k0 + k, wv[IN ? 1 : 0]);
+          if (PAIR) load_piece(w_e + (long long)(p.N + n) * p.K + k0 + k, wv[PAIR ? 1 : 0]);
 #pragma unroll
           for (int r = 0; r < MF_ROWS; ++r) {
             float xv[8];
@@ -480,7 +503,7 @@ moe_expert_few_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* 
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
               acc[0][col][r] = fmaf(xv[u], wv[0][u], acc[0][col][r]);
-              if (IN) acc[IN ? 1 : 0][col][r] = fmaf(xv[u], wv[IN ? 1 : 0][u], acc[IN ? 1 : 0][col][r]);
+              if (PAIR) acc[PAIR ? 1 : 0][col][r] = fmaf(xv[u], wv[PAIR ? 1 : 0][u], acc[PAIR ? 1 : 0][col][r]);
             }
           }
         }
@@ -491,12 +514,13 @@ moe_expert_few_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* 
 #pragma unroll
       for (int r = 0; r < MF_ROWS; ++r) {
         const float g = warp_sum(acc[0][col][r]);
-        const float u = IN ? warp_sum(acc[IN ? 1 : 0][col][r]) : 0.f;
+        const float u = PAIR ? warp_sum(acc[PAIR ? 1 : 0][col][r]) : 0.f;
         const int n = n0 + col;
         if (lane == 0 && r < rows && n < p.N) {
           const long long row = first + r0 + r;
           if (IN)
-            reinterpret_cast<__nv_bfloat16*>(out)[row * p.N + n] = __float2bfloat16_rn(gated_pair(g, u, p.act, p.limit));
+            reinterpret_cast<__nv_bfloat16*>(out)[row * p.N + n] =
+                __float2bfloat16_rn(PAIR ? gated_pair(g, u, p.act, p.limit) : apply_activation(g, p.act));
           else
             reinterpret_cast<float*>(out)[row * p.N + n] = g * p.pair_weight[p.order[row]];
         }
@@ -504,10 +528,12 @@ moe_expert_few_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* 
   }
 }
 
-// stream[t, c] += sum_j part[place[t * top + j], c]
+// stream[t, c] += sum_j part[place[t * top + j], c]; a pair whose expert is `n_stored` or more adds weight * input[t, c]
+// instead (`ids` null: every pair has a row in `part`)
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ part, const int* __restrict__ place, float* __restrict__ stream,
-                   long long n_tokens, int top, int width) {
+                   long long n_tokens, int top, int width, const int* __restrict__ ids, const float* __restrict__ weights,
+                   const float* __restrict__ input, int n_stored) {
   pdl_trigger();
   pdl_wait();
   const long long total = n_tokens * width;
@@ -515,7 +541,10 @@ moe_combine_kernel(const float* __restrict__ part, const int* __restrict__ place
     const long long t = i / width;
     const int c = (int)(i - t * width);
     float sum = 0.f;
-    for (int j = 0; j < top; ++j) sum += part[(long long)place[t * top + j] * width + c];
+    for (int j = 0; j < top; ++j) {
+      if (ids != nullptr && ids[t * top + j] >= n_stored) sum = fmaf(weights[t * top + j], input[i], sum);
+      else sum += part[(long long)place[t * top + j] * width + c];
+    }
     stream[i] += sum;
   }
 }
@@ -523,8 +552,8 @@ moe_combine_kernel(const float* __restrict__ part, const int* __restrict__ place
 }  // namespace bt
 
 extern "C" int bt_moe_route(const void* x, long long x_row_stride, const void* router, int n_tokens, int K, int E, int top,
-                            int n_groups, int keep, float scale, int* ids, float* weights, int dtype,
-                            cudaStream_t stream) {
+                            int n_groups, int keep, float scale, int softmax, const float* choice_bias, int normalise,
+                            int* ids, float* weights, int dtype, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_tokens >= 0 && K > 0 && E > 0 && E <= 1024 && top > 0 && top <= 32 && n_groups > 0 && E % n_groups == 0 &&
                keep > 0 && keep <= n_groups && top <= keep * (E / n_groups),
@@ -541,7 +570,8 @@ extern "C" int bt_moe_route(const void* x, long long x_row_stride, const void* r
   };
 #define BT_ROUTE(T, NP)                                                                                              \
   BT_PDL_OK("moe_route", launch_pdl(moe_route_kernel<T, NP>, grid, block, smem, stream, 1, (const T*)x, x_row_stride, \
-                                    (const T*)router, n_tokens, K, E, top, n_groups, keep, scale, ids, weights))
+                                    (const T*)router, n_tokens, K, E, top, n_groups, keep, scale, softmax, choice_bias, \
+                                    normalise, ids, weights))
   if (dtype == kF32) {
     const int np = pieces_of(4);
     if (np == 1) BT_ROUTE(float, 1); else if (np == 2) BT_ROUTE(float, 2); else if (np == 4) BT_ROUTE(float, 4);
@@ -570,14 +600,16 @@ extern "C" int bt_moe_sort(const int* ids, int total, int E, int* offsets, int* 
 }
 
 // first: 1 = the experts' first product (a: the tokens' rows [tokens, K]; w: [E][2N][K]; out: [pairs, N] of the
-// compute type), 0 = the second (a: [pairs, K]; w: [E][N][K]; out: [pairs, N] 32-bit, times the pair's weight).
+// compute type), 2 = the first product of experts without a gate (w: [E][N][K]; out = act(product)), 0 = the second (a:
+// [pairs, K]; w: [E][N][K]; out: [pairs, N] 32-bit, times the pair's weight).  E counts the experts with tensors; the
+// sorted rows of pairs with a higher number lie behind theirs and are left alone.
 extern "C" int bt_moe_expert(int first, const void* a, long long a_row_stride, const void* w, void* out,
                              const int* offsets, const int* tile_first, const int* order, const float* pair_weight,
                              int pairs, int E, int top, int K, int N, int act, float limit, int tensor_cores, int dtype,
                              cudaStream_t stream) {
   using namespace bt;
-  BT_CHECK(pairs >= 0 && E > 0 && top > 0 && K > 0 && N > 0, "moe_expert: bad sizes pairs=%d experts=%d K=%d N=%d", pairs,
-           E, K, N);
+  BT_CHECK(pairs >= 0 && E > 0 && top > 0 && K > 0 && N > 0 && first >= 0 && first <= 2,
+           "moe_expert: bad sizes pairs=%d experts=%d K=%d N=%d", pairs, E, K, N);
   if (pairs == 0) return 0;
   MoeArgs p;
   p.offsets = offsets; p.tile_first = tile_first; p.order = order; p.pair_weight = pair_weight;
@@ -590,41 +622,55 @@ extern "C" int bt_moe_expert(int first, const void* a, long long a_row_stride, c
   if (pieces && tensor_cores && pairs <= 16 * E && E <= 65535) {
     // few rows an expert (a decode step): every expert's weights streamed once per 8 of its rows
     const dim3 few((N + MF_COLS - 1) / MF_COLS, E);
-    if (first)
-      BT_PDL_OK("moe_expert", launch_pdl(moe_expert_few_kernel<true>, few, dim3(128), 0, stream, 1,
+    if (first == kMoeInPair)
+      BT_PDL_OK("moe_expert", launch_pdl(moe_expert_few_kernel<kMoeInPair>, few, dim3(128), 0, stream, 1,
+                                         (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, out, p));
+    else if (first == kMoeInPlain)
+      BT_PDL_OK("moe_expert", launch_pdl(moe_expert_few_kernel<kMoeInPlain>, few, dim3(128), 0, stream, 1,
                                          (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, out, p));
     else
-      BT_PDL_OK("moe_expert", launch_pdl(moe_expert_few_kernel<false>, few, dim3(128), 0, stream, 1,
+      BT_PDL_OK("moe_expert", launch_pdl(moe_expert_few_kernel<kMoeOut>, few, dim3(128), 0, stream, 1,
                                          (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, out, p));
     return 0;
   }
   if (dtype == kBF16 && tensor_cores && K % 8 == 0 && a_row_stride % 8 == 0 && (unsigned long long)a % 16 == 0 &&
       (unsigned long long)w % 16 == 0) {
-    if (first)
-      BT_PDL_OK("moe_expert", launch_pdl(moe_expert_mma_kernel<true>, grid, dim3(128), 0, stream, 1,
+    if (first == kMoeInPair)
+      BT_PDL_OK("moe_expert", launch_pdl(moe_expert_mma_kernel<kMoeInPair>, grid, dim3(128), 0, stream, 1,
+                                         (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, out, p));
+    else if (first == kMoeInPlain)
+      BT_PDL_OK("moe_expert", launch_pdl(moe_expert_mma_kernel<kMoeInPlain>, grid, dim3(128), 0, stream, 1,
                                          (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, out, p));
     else
-      BT_PDL_OK("moe_expert", launch_pdl(moe_expert_mma_kernel<false>, grid, dim3(128), 0, stream, 1,
+      BT_PDL_OK("moe_expert", launch_pdl(moe_expert_mma_kernel<kMoeOut>, grid, dim3(128), 0, stream, 1,
                                          (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, out, p));
     return 0;
   }
 #define BT_MOE(T, FIRST) \
   BT_PDL_OK("moe_expert", launch_pdl(moe_expert_simt_kernel<T, FIRST>, grid, dim3(256), 0, stream, 1, (const T*)a, (const T*)w, out, p))
-  if (dtype == kF32) { if (first) BT_MOE(float, true); else BT_MOE(float, false); }
-  else if (dtype == kBF16) { if (first) BT_MOE(__nv_bfloat16, true); else BT_MOE(__nv_bfloat16, false); }
+#define BT_MOE_MODES(T)                                                                          \
+  do {                                                                                           \
+    if (first == kMoeInPair) BT_MOE(T, kMoeInPair); else if (first == kMoeInPlain) BT_MOE(T, kMoeInPlain); \
+    else BT_MOE(T, kMoeOut);                                                                     \
+  } while (0)
+  if (dtype == kF32) BT_MOE_MODES(float);
+  else if (dtype == kBF16) BT_MOE_MODES(__nv_bfloat16);
   else return fail("moe_expert: unknown dtype %d", dtype);
+#undef BT_MOE_MODES
 #undef BT_MOE
   return 0;
 }
 
 extern "C" int bt_moe_combine(const float* part, const int* place, float* stream_rows, long long n_tokens, int top,
-                              int width, cudaStream_t stream) {
+                              int width, const int* ids, const float* weights, const float* input, int n_stored,
+                              cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_tokens >= 0 && top > 0 && width > 0, "moe_combine: bad sizes");
+  BT_CHECK(ids == nullptr || (weights != nullptr && input != nullptr), "moe_combine: pairs that hand the input on need weights and the input");
   if (n_tokens == 0) return 0;
   const long long total = n_tokens * width;
   const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
   BT_PDL_OK("moe_combine", launch_pdl(moe_combine_kernel, dim3(blocks), dim3(256), 0, stream, 1, part, place, stream_rows,
-                                      n_tokens, top, width));
+                                      n_tokens, top, width, ids, weights, input, n_stored));
   return 0;
 }

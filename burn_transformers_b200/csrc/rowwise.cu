@@ -309,7 +309,7 @@ namespace bt {
 template <typename TOut>
 __global__ void __launch_bounds__(128)
 rmsnorm_add_kernel(const float* __restrict__ x, const float* __restrict__ weight, float* __restrict__ stream_rows,
-                   const float* __restrict__ next_weight, TOut* __restrict__ next_out, int width, float eps) {
+                   const float* __restrict__ next_weight, TOut* __restrict__ next_out, int width, float eps, float factor) {
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
@@ -321,11 +321,15 @@ rmsnorm_add_kernel(const float* __restrict__ x, const float* __restrict__ weight
   const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
   float ss2 = 0.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    const float v = dst[c] + src[c] * inv * weight[c];
+    const float v = fmaf(factor, src[c] * inv * weight[c], dst[c]);
     dst[c] = v;
     ss2 = fmaf(v, v, ss2);
   }
   if (next_out == nullptr) return;
+  if (next_weight == nullptr) {       // the next sublayer reads the new row as it is, in its own element type
+    for (int c = threadIdx.x; c < width; c += blockDim.x) next_out[r * width + c] = from_float<TOut>(dst[c]);
+    return;
+  }
   const float inv2 = 1.f / sqrtf(block_sum(ss2, scratch) / (float)width + eps);
   for (int c = threadIdx.x; c < width; c += blockDim.x)       // (a thread reads back what it wrote itself)
     next_out[r * width + c] = from_float<TOut>(dst[c] * inv2 * next_weight[c]);
@@ -393,21 +397,69 @@ rotary_half_kernel(const T* __restrict__ src, long long src_row_stride, float* _
   for (int i = threadIdx.x; i < tail; i += blockDim.x) d_row[base + i] = to_float(s_row[base + i]);
 }
 
+// out[t] = x[t] + (x[t - 1] - x[t]) * shift for the rows of a step, a sequence's rows one after another; the row before a
+// sequence's first row of the step is state[slot] (zeros for a new sequence), which then becomes the sequence's last
+// row.  A block a row; the block of a sequence's last row also does its first row, which reads the state, and writes the
+// state afterwards, so that nothing reads what another block replaces.
+template <typename TOut>
+__global__ void __launch_bounds__(128)
+token_shift_kernel(const float* __restrict__ x, const float* __restrict__ shift, float* __restrict__ state,
+                   const int* __restrict__ slots, const int* __restrict__ seq_start, const int* __restrict__ token_seq,
+                   TOut* __restrict__ out, int width) {
+  pdl_trigger();
+  pdl_wait();
+  const long long t = blockIdx.x;
+  const int seq = token_seq[t];
+  const long long first = seq_start[seq], last = (long long)seq_start[seq + 1] - 1;
+  float* kept = state + (long long)slots[seq] * width;
+  if (t != first || t == last) {
+    const float* cur = x + t * width;
+    const float* prev = t == first ? kept : cur - width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+      out[t * width + c] = from_float<TOut>(fmaf(prev[c] - cur[c], shift[c], cur[c]));
+  }
+  if (t != last) return;
+  if (first != last) {
+    const float* cur = x + first * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+      out[first * width + c] = from_float<TOut>(fmaf(kept[c] - cur[c], shift[c], cur[c]));
+  }
+  const float* cur = x + last * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) kept[c] = cur[c];      // (a thread read kept[c] itself above)
+}
+
 }  // namespace bt
 
+extern "C" int bt_token_shift(const float* x, const float* shift, float* state, const int* slots, const int* seq_start,
+                              const int* token_seq, void* out, int out_dtype, long long n_rows, int width,
+                              cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(n_rows >= 0 && n_rows < (1ll << 31) && width > 0, "token_shift: bad sizes rows=%lld width=%d", n_rows, width);
+  if (n_rows == 0) return 0;
+  if (out_dtype == kBF16)
+    BT_PDL_OK("token_shift", launch_pdl(token_shift_kernel<__nv_bfloat16>, dim3((unsigned)n_rows), dim3(128), 0, stream, 1, x,
+                                        shift, state, slots, seq_start, token_seq, (__nv_bfloat16*)out, width));
+  else if (out_dtype == kF32)
+    BT_PDL_OK("token_shift", launch_pdl(token_shift_kernel<float>, dim3((unsigned)n_rows), dim3(128), 0, stream, 1, x, shift,
+                                        state, slots, seq_start, token_seq, (float*)out, width));
+  else
+    return fail("token_shift: unknown dtype %d", out_dtype);
+  return 0;
+}
+
 extern "C" int bt_rmsnorm_add(const float* x, const float* weight, float* stream_rows, const float* next_weight,
-                              void* next_out, int next_dtype, long long n_rows, int width, float eps, cudaStream_t stream) {
+                              void* next_out, int next_dtype, long long n_rows, int width, float eps, float factor,
+                              cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_rows >= 0 && n_rows < (1ll << 31) && width > 0, "rmsnorm_add: bad sizes rows=%lld width=%d", n_rows, width);
-  BT_CHECK(next_out == nullptr || (next_weight != nullptr && (next_dtype == kF32 || next_dtype == kBF16)),
-           "rmsnorm_add: the second norm needs a weight and a known dtype");
+  BT_CHECK(next_out == nullptr || next_dtype == kF32 || next_dtype == kBF16, "rmsnorm_add: the next rows need a known dtype");
   if (n_rows == 0) return 0;
   if (next_out != nullptr && next_dtype == kBF16)
     BT_PDL_OK("rmsnorm_add", launch_pdl(rmsnorm_add_kernel<__nv_bfloat16>, dim3((unsigned)n_rows), dim3(128), 0, stream, 1, x,
-                                        weight, stream_rows, next_weight, (__nv_bfloat16*)next_out, width, eps));
+                                        weight, stream_rows, next_weight, (__nv_bfloat16*)next_out, width, eps, factor));
   else
     BT_PDL_OK("rmsnorm_add", launch_pdl(rmsnorm_add_kernel<float>, dim3((unsigned)n_rows), dim3(128), 0, stream, 1, x, weight,
-                                        stream_rows, next_weight, (float*)next_out, width, eps));
+                                        stream_rows, next_weight, (float*)next_out, width, eps, factor));
   return 0;
 }
 

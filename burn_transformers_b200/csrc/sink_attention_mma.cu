@@ -33,6 +33,7 @@ struct SinkAttentionArgs {
   const float* sink;
   int dq, dv;
   float scale;
+  int window;      // > 0: a row sees the last `window` positions up to its own
 };
 
 // VCT: the most value channels (a multiple of 16)
@@ -89,7 +90,8 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(SinkAttentionAr
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
-  load_tile(0, 0);
+  const int kt_first = p.window > 0 ? max(0, t0 - p.window + 1) / SA_KT : 0;      // tiles before it: outside every row's window
+  load_tile(kt_first, kt_first & 1);
   float m_run[2], l_run[2];
   const bool has_sink = p.sink != nullptr;
 #pragma unroll
@@ -106,7 +108,7 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(SinkAttentionAr
   const int row0 = t0 + warp * 16 + g;               // this lane's rows: row0 and row0 + 8 (positions inside the sequence)
   const unsigned q_addr = ds_smem(q_s + (warp * 16 + (lane & 15)) * ldq + (lane >> 4) * 8);
   const int blk = lane >> 3;
-  for (int kt = 0; kt < n_tiles; ++kt) {
+  for (int kt = kt_first; kt < n_tiles; ++kt) {
     const int buf = kt & 1;
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();
@@ -140,7 +142,7 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(SinkAttentionAr
         const int j = j0 + n * 8 + qd * 2 + (e & 1);
         const int rr = e >> 1;
         const int row = row0 + 8 * rr;
-        const float val = (row < n_new && j <= row) ? s[n][e] * scale_log2 : -INFINITY;
+        const float val = (row < n_new && j <= row && (p.window <= 0 || row - j < p.window)) ? s[n][e] * scale_log2 : -INFINITY;
         s[n][e] = val;
         mx[rr] = fmaxf(mx[rr], val);
       }
@@ -233,7 +235,7 @@ extern "C" int bt_sink_attention(const void* q, long long q_row, int q_head, con
                                  const void* v, long long v_row, int v_head, const void* gate, long long gate_row,
                                  int gate_head, void* out, long long out_row, int out_head, const int* seq_start,
                                  const float* sink, int n_seqs, int max_new, int n_heads, int dq, int dv, float scale,
-                                 cudaStream_t stream) {
+                                 int window, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(bt_sink_attention_supports(dq, dv, q_row, q_head, k_row, k_head, v_row, v_head, gate_row, gate_head, out_row,
                                       out_head),
@@ -248,7 +250,7 @@ extern "C" int bt_sink_attention(const void* q, long long q_row, int q_head, con
   p.gate = (const __nv_bfloat16*)gate; p.out = (__nv_bfloat16*)out;
   p.q_row = q_row; p.k_row = k_row; p.v_row = v_row; p.gate_row = gate_row; p.out_row = out_row;
   p.q_head = q_head; p.k_head = k_head; p.v_head = v_head; p.gate_head = gate_head; p.out_head = out_head;
-  p.seq_start = seq_start; p.sink = sink; p.dq = dq; p.dv = dv; p.scale = scale;
+  p.seq_start = seq_start; p.sink = sink; p.dq = dq; p.dv = dv; p.scale = scale; p.window = window;
   const int dqp = (dq + 15) & ~15, dvp = (dv + 15) & ~15;
   const size_t smem = (size_t)(SA_BM + 2 * SA_KT) * (dqp + SA_PAD) * 2 + (size_t)2 * SA_KT * (dvp + SA_PAD) * 2;
   const dim3 grid((max_new + SA_BM - 1) / SA_BM, n_heads, n_seqs), block(128);

@@ -55,6 +55,9 @@ class ModelPlan:
     sources: dict = dataclasses.field(default_factory=dict)
     # learned vectors that calls of the schedule add to the stream before they run (`LayerCall.opens`)
     stream_vectors: Part | None = None
+    # tensors that live for one step and that layers hand to later layers of the same step: name -> (channels, dtype);
+    # every step gets `ctx.shared[name]`, [tokens, channels], out of its scratch memory before the first layer runs
+    step_tensors: dict = dataclasses.field(default_factory=dict)
 
     def __post_init__(self):
         for index, call in enumerate(self.schedule):
@@ -106,6 +109,8 @@ class ModelPlan:
         """Runs the step's tokens through every layer call; returns 32-bit logits at the wanted rows."""
         residual = ctx.ws.take((ctx.n_tokens, self.width), torch.float32)
         self.embedding.forward(ctx, self.positions, residual)
+        ctx.shared = {name: ctx.ws.take((ctx.n_tokens, channels), dtype)
+                      for name, (channels, dtype) in self.step_tensors.items()}
         for index, call in enumerate(self.schedule):
             entry, owns = self.cache_entry(index)
             if call.opens is not None:

@@ -97,6 +97,7 @@ class StepContext:
         self.tables = tables            # per cache group: [n_seqs, table_width] page ids
         self.program = None             # set while a fused decode step is recorded (engine.program.DecodeProgram)
         self.side = None                # a SideWork: a second stream for work nothing later in the step waits for
+        self.shared = {}                # the step's tensors that layers hand to later layers (ModelPlan.step_tensors)
         # the same facts as Python lists, for parts that plan on the host
         self.host_slots, self.host_seq_start, self.host_past_len = host_slots, host_seq_start, host_past_len
 

@@ -713,7 +713,7 @@ def latent_attention_rows(rank, rot, dtype, tensor_cores=True) -> int:
 
 
 def latent_attention(q, out, pool, table, table_len, seq_start, past_len, *, n_tokens, n_seqs, max_new, n_heads, rank,
-                     rot, scale, sink=None, n_splits=1, scratch=None, tensor_cores=True, merge=True):
+                     rot, scale, sink=None, n_splits=1, scratch=None, tensor_cores=True, merge=True, window=0):
     """Causal attention of the step's tokens over their sequences' latent pages.
 
     q: [tokens, heads * (rank + rot)] (per head: the query carried into the latent space, then its rotated part);
@@ -722,7 +722,8 @@ def latent_attention(q, out, pool, table, table_len, seq_start, past_len, *, n_t
     cut into that many runs whose partial results meet in `scratch` (32-bit, latent_attention_scratch_floats).
     bfloat16 runs on tensor cores where the shape allows it (rank + rot a multiple of 8, rank a multiple of 8, 16 or 32
     up to 128, 256, 512); `tensor_cores=False` keeps it on the 32-bit multiply-add kernel that every other case takes.
-    `merge=False` (with splits) leaves the partial results in `scratch` for latent_decode_finish to join."""
+    `merge=False` (with splits) leaves the partial results in `scratch` for latent_decode_finish to join.  `window` > 0:
+    a token sees the last `window` positions up to its own (the splits cut the tiles from its first visible key on)."""
     dk = rank + rot
     _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * dk))
     _need(out, "out", q.dtype, (None, n_heads * rank))
@@ -747,7 +748,7 @@ def latent_attention(q, out, pool, table, table_len, seq_start, past_len, *, n_t
         _ptr(q), c_longlong(q.shape[1]), _ptr(pool), _ptr(table), c_int(table.shape[1]), c_int(table_len),
         c_int(PAGE_SIZE), _ptr(seq_start), _ptr(past_len), _ptr(sink), _ptr(out), c_longlong(out.shape[1]),
         _ptr(scratch if n_splits > 1 else None), c_int(n_tokens), c_int(n_seqs), c_int(max_new), c_int(n_heads),
-        c_int(rank), c_int(rot), c_float(scale), c_int(n_splits), c_int(1 if tensor_cores else 0),
+        c_int(rank), c_int(rot), c_float(scale), c_int(n_splits), c_int(window), c_int(1 if tensor_cores else 0),
         c_int(1 if merge else 0), c_int(_code(q.dtype)), _stream()))
 
 
@@ -945,12 +946,18 @@ def mlstm_scan_fuses(dim: int, vdim: int) -> bool:
     return bool(library().bt_mlstm_scan_fuses(c_int(dim), c_int(vdim)))
 
 
-def moe_route(x, router, ids, weights, *, n_tokens, top, n_groups=1, keep=1, scale=1.0):
+def moe_route(x, router, ids, weights, *, n_tokens, top, n_groups=1, keep=1, scale=1.0, rule="sigmoid", choice_bias=None,
+              normalise=True):
     """Per token the `top` experts with the largest sigmoid(router x) among the experts of the `keep` best of `n_groups`
     groups of neighbours (a group's score: the sum of its two largest), and their weights score / (sum + 1e-20) * scale.
     x [tokens, K] and router [experts, K] in the compute type, the products summed in 32-bit; ids int32 and weights
-    32-bit, [tokens, top]."""
+    32-bit, [tokens, top].  `rule` "softmax": the scores are softmax(router x) over all experts.  `choice_bias` [experts]
+    (32-bit) is added to the scores for the choice only; without `normalise` a weight is the chosen score as it is."""
     e, k = router.shape
+    if rule not in ("sigmoid", "softmax"):
+        raise ShapeError(f"moe_route: unknown rule {rule!r}")
+    if choice_bias is not None:
+        _need(choice_bias, "choice_bias", torch.float32, (e,))
     _need(x, "x", (torch.float32, torch.bfloat16), (None, k))
     _need(router, "router", x.dtype)
     _need(ids, "ids", torch.int32, (None, top))
@@ -959,8 +966,9 @@ def moe_route(x, router, ids, weights, *, n_tokens, top, n_groups=1, keep=1, sca
         raise ShapeError(f"moe_route: {n_tokens} tokens asked of shorter tensors")
     _work(2.0 * n_tokens * e * k, n_tokens * k * x.element_size())
     _check(library().bt_moe_route(_ptr(x), c_longlong(x.stride(0)), _ptr(router), c_int(n_tokens), c_int(k), c_int(e),
-                                  c_int(top), c_int(n_groups), c_int(keep), c_float(scale), _ptr(ids), _ptr(weights),
-                                  c_int(_code(x.dtype)), _stream()))
+                                  c_int(top), c_int(n_groups), c_int(keep), c_float(scale),
+                                  c_int(1 if rule == "softmax" else 0), _ptr(choice_bias), c_int(1 if normalise else 0),
+                                  _ptr(ids), _ptr(weights), c_int(_code(x.dtype)), _stream()))
 
 
 def moe_sort(ids, offsets, tile_first, order, place, *, pairs, n_experts):
@@ -976,29 +984,39 @@ def moe_sort(ids, offsets, tile_first, order, place, *, pairs, n_experts):
 
 
 def moe_expert(first: bool, a, w, out, offsets, tile_first, order, pair_weight, *, pairs, top, activation=None,
-               limit: float = 0.0, tensor_cores: bool = True):
+               limit: float = 0.0, tensor_cores: bool = True, gated: bool = True):
     """One of the experts' two products over the sorted rows (csrc/moe.cu).  first: a [tokens, K] (gathered by the
     pair's token), w [experts, 2 N, K] (gate rows, then up rows), out [pairs, N] = pair rule(gate, up).  second: a
-    [pairs, K], w [experts, N, K], out [pairs, N] 32-bit = the pair's weight times the product."""
+    [pairs, K], w [experts, N, K], out [pairs, N] 32-bit = the pair's weight times the product.  first without `gated`:
+    w [experts, N, K], out [pairs, N] = activation(product).  `w` holds the experts with tensors; pairs whose expert has a
+    higher number (sorted behind them) are left alone."""
     e, rows_w, k = w.shape
-    n = rows_w // 2 if first else rows_w
+    n = rows_w // 2 if first and gated else rows_w
     _need(a, "a", (torch.float32, torch.bfloat16), (None, k))
     _need(w, "w", a.dtype)
     _need(out, "out", a.dtype if first else torch.float32, (None, n))
     if out.shape[0] < pairs or (not first and a.shape[0] < pairs):
         raise ShapeError(f"moe_expert: {pairs} rows asked of shorter tensors")
-    if activation not in PAIR_RULES:
+    if activation not in (PAIR_RULES if gated else ACTIVATIONS):
         raise ShapeError(f"moe_expert: unknown activation {activation!r}")
     _work(2.0 * pairs * rows_w * k, w.numel() * w.element_size() + pairs * (k * a.element_size() + n * out.element_size()))
-    _check(library().bt_moe_expert(c_int(1 if first else 0), _ptr(a), c_longlong(a.stride(0)), _ptr(w), _ptr(out),
+    _check(library().bt_moe_expert(c_int((1 if gated else 2) if first else 0), _ptr(a), c_longlong(a.stride(0)), _ptr(w), _ptr(out),
                                    _ptr(offsets), _ptr(tile_first), _ptr(order), _ptr(pair_weight), c_int(pairs), c_int(e),
                                    c_int(top), c_int(k), c_int(n), c_int(PAIR_RULES[activation]), c_float(limit),
                                    c_int(1 if tensor_cores else 0), c_int(_code(a.dtype)), _stream()))
 
 
-def moe_combine(part, place, stream_rows, *, n_tokens, top):
-    """stream_rows[t] += sum over the token's `top` pairs of part[place[t * top + j]], in that order (32-bit)."""
+def moe_combine(part, place, stream_rows, *, n_tokens, top, ids=None, weights=None, identity_input=None, n_stored=0):
+    """stream_rows[t] += sum over the token's `top` pairs of part[place[t * top + j]], in that order (32-bit).  With `ids`
+    ([tokens, top], the pairs' experts), a pair whose expert is `n_stored` or more adds weights[t, j] * identity_input[t]
+    instead (an expert without tensors that hands its input on; identity_input: contiguous 32-bit [tokens, width])."""
     width = stream_rows.shape[1]
+    if ids is not None:
+        _need(ids, "ids", torch.int32, (None, top))
+        _need(weights, "weights", torch.float32, (None, top))
+        _need(identity_input, "identity_input", torch.float32, (None, width))
+        if min(ids.shape[0], weights.shape[0], identity_input.shape[0]) < n_tokens:
+            raise ShapeError(f"moe_combine: {n_tokens} tokens asked of shorter tensors")
     _need(part, "part", torch.float32, (None, width))
     _need(place, "place", torch.int32)
     _need(stream_rows, "stream_rows", torch.float32)
@@ -1006,7 +1024,8 @@ def moe_combine(part, place, stream_rows, *, n_tokens, top):
         raise ShapeError(f"moe_combine: {n_tokens} tokens asked of shorter tensors")
     _work(0.0, 4.0 * n_tokens * width * (top + 2))
     _check(library().bt_moe_combine(_ptr(part), _ptr(place), _ptr(stream_rows), c_longlong(n_tokens), c_int(top),
-                                    c_int(width), _stream()))
+                                    c_int(width), _ptr(ids), _ptr(weights), _ptr(identity_input), c_int(n_stored),
+                                    _stream()))
 
 
 def scale_(x, factor: float):
@@ -1051,7 +1070,7 @@ def sink_attention_supports(q, k, v, gate, out) -> bool:
                                                      c_int(gh), c_longlong(orow), c_int(oh)))
 
 
-def sink_attention(q, k, v, out, seq_start, *, n_seqs, max_new, scale, sink=None, gate=None):
+def sink_attention(q, k, v, out, seq_start, *, n_seqs, max_new, scale, sink=None, gate=None, window=0):
     """Causal multi-head attention of sequences that start at position 0, on tensor cores (bfloat16): token t of a
     sequence sees the sequence's tokens up to itself.  q, k: views [tokens, heads, dq]; v, out, gate: views
     [tokens, heads, dv].  `sink` [heads] adds exp(sink_h) to head h's softmax denominator; `gate` multiplies the result by
@@ -1068,7 +1087,8 @@ def sink_attention(q, k, v, out, seq_start, *, n_seqs, max_new, scale, sink=None
     _check(library().bt_sink_attention(_ptr(q), c_longlong(qr), c_int(qh), _ptr(k), c_longlong(kr), c_int(kh), _ptr(v),
                                        c_longlong(vr), c_int(vh), _ptr(gate), c_longlong(gr), c_int(gh), _ptr(out),
                                        c_longlong(orow), c_int(oh), _ptr(seq_start), _ptr(sink), c_int(n_seqs),
-                                       c_int(max_new), c_int(heads), c_int(dq), c_int(dv), c_float(scale), _stream()))
+                                       c_int(max_new), c_int(heads), c_int(dq), c_int(dv), c_float(scale), c_int(window),
+                                       _stream()))
 
 
 def latent_decode_prep(proj, q_off, latent_off, uk_heads, norm_weight, eps, positions, token_seq, inv_freq, rot_dims, table,
@@ -1123,26 +1143,28 @@ def latent_decode_finish(uv_heads, out, *, n_tokens, n_splits, scratch=None, mix
 
 # ---- a sublayer's normed result into the stream; the polynomial activation; the half-split rotation -----------------
 
-def rmsnorm_add(x, weight, stream_rows, eps: float, *, n_rows, next_weight=None, next_out=None):
-    """stream_rows[r] += x[r] / sqrt(mean(x[r]^2) + eps) * weight for contiguous 32-bit [rows, width] tensors.  With
-    `next_weight` and `next_out` ([rows, width], 32-bit or bfloat16) the updated row is normed again into next_out."""
+def rmsnorm_add(x, weight, stream_rows, eps: float, *, n_rows, next_weight=None, next_out=None, factor: float = 1.0):
+    """stream_rows[r] += factor * x[r] / sqrt(mean(x[r]^2) + eps) * weight for contiguous 32-bit [rows, width] tensors.
+    With `next_out` ([rows, width], 32-bit or bfloat16) the updated row is also written there: normed again with
+    `next_weight`, or, without one, as it is (rounded to next_out's type)."""
     width = weight.shape[0]
     _need(x, "x", torch.float32, (None, width))
     _need(stream_rows, "stream_rows", torch.float32, (None, width))
     _need(weight, "weight", torch.float32, (width,))
     if min(x.shape[0], stream_rows.shape[0]) < n_rows:
         raise ShapeError(f"rmsnorm_add: {n_rows} rows asked of shorter tensors")
-    if (next_weight is None) != (next_out is None):
-        raise ShapeError("rmsnorm_add: the second norm needs both a weight and a place for its rows")
+    if next_weight is not None and next_out is None:
+        raise ShapeError("rmsnorm_add: the second norm needs a place for its rows")
     if next_out is not None:
-        _need(next_weight, "next_weight", torch.float32, (width,))
+        if next_weight is not None:
+            _need(next_weight, "next_weight", torch.float32, (width,))
         _need(next_out, "next_out", (torch.float32, torch.bfloat16), (None, width))
         if next_out.shape[0] < n_rows:
             raise ShapeError(f"rmsnorm_add: {n_rows} rows asked of next_out[{next_out.shape[0]}]")
     _work(0.0, n_rows * width * (12.0 + (next_out.element_size() if next_out is not None else 0)))
     _check(library().bt_rmsnorm_add(_ptr(x), _ptr(weight), _ptr(stream_rows), _ptr(next_weight), _ptr(next_out),
                                     c_int(_code(next_out.dtype)) if next_out is not None else c_int(0),
-                                    c_longlong(n_rows), c_int(width), c_float(eps), _stream()))
+                                    c_longlong(n_rows), c_int(width), c_float(eps), c_float(factor), _stream()))
 
 
 def polynorm(x, coef, out, eps: float, *, n_rows):
@@ -1350,3 +1372,84 @@ def selective_scan(x, z, dt, low, b_off, c_off, a_log, d_skip, state, slots, seq
                                        c_int(n_seqs), c_int(channels), c_int(n_state), c_float(out_scale), c_int(piece),
                                        c_int(max_pieces), _ptr(scratch) if piece else c_void_p(0),
                                        c_int(_code(x.dtype)), _stream()))
+
+
+# ---- token shift, sigmoid attention -----------------------------------------------------------------------------------
+
+def token_shift(x, shift, state, slots, seq_start, token_seq, out, *, n_rows):
+    """out[t] = x[t] + (x[t - 1] - x[t]) * shift over the step's rows (32-bit arithmetic, rounded to out's type); the row
+    before a sequence's first row of the step is state[slot], which afterwards holds the sequence's last row of x.
+    x: contiguous 32-bit [rows, width]; shift: 32-bit [width]; state: 32-bit [slots, width]; out: [rows, width]."""
+    width = shift.shape[0]
+    _need(x, "x", torch.float32, (None, width))
+    _need(shift, "shift", torch.float32, (width,))
+    _need(state, "state", torch.float32, (None, width))
+    _need(out, "out", (torch.float32, torch.bfloat16), (None, width))
+    if min(x.shape[0], out.shape[0]) < n_rows:
+        raise ShapeError(f"token_shift: {n_rows} rows asked of shorter tensors")
+    _work(0.0, n_rows * width * (8.0 + out.element_size()))
+    _check(library().bt_token_shift(_ptr(x), _ptr(shift), _ptr(state), _ptr(slots), _ptr(seq_start), _ptr(token_seq),
+                                    _ptr(out), c_int(_code(out.dtype)), c_longlong(n_rows), c_int(width), _stream()))
+
+
+def sigmoid_attention_prep(proj, q_weight, k_weight, eps, positions, token_seq, inv_freq, rot_dims, table, table_len, pool,
+                           *, n_tokens, n_heads, n_kv_heads, dim, vdim, mix=None, v_other=None, v_publish=None):
+    """Prepares a step's projections `proj` [tokens, (heads + kv_heads) * dim + kv_heads * vdim] (queries, keys, values)
+    for sigmoid_attention: query and key heads divided by their root mean square times `q_weight` / `k_weight` [dim] and
+    their first `rot_dims` channels turned by the position (channel i with channel i + rot_dims / 2, angle position *
+    inv_freq[i]); value heads divided by their root mean square and, with `v_other` (32-bit [tokens, kv_heads * vdim]) and
+    `mix` (a 32-bit number on the device), replaced by (1 - mix) v + mix v_other; `v_publish` receives the values as
+    they end up.  Queries are rewritten in place; keys and values go to the token's rows of `pool`
+    [pages, kv_heads, PAGE_SIZE, dim + vdim]."""
+    width = (n_heads + n_kv_heads) * dim + n_kv_heads * vdim
+    _need(proj, "proj", (torch.float32, torch.bfloat16), (None, width))
+    _need(pool, "pool", proj.dtype, (None, n_kv_heads, PAGE_SIZE, dim + vdim))
+    _need(q_weight, "q_weight", torch.float32, (dim,))
+    _need(k_weight, "k_weight", torch.float32, (dim,))
+    _need(inv_freq, "inv_freq", torch.float32)
+    _need(table, "table", torch.int32)
+    if inv_freq.numel() < rot_dims // 2 or proj.shape[0] < n_tokens:
+        raise ShapeError("sigmoid_attention_prep: too few rows or frequencies")
+    if (v_other is None) != (mix is None):
+        raise ShapeError("sigmoid_attention_prep: mixing needs both the other values and the mixing number")
+    for name, t in (("v_other", v_other), ("v_publish", v_publish)):
+        if t is not None:
+            _need(t, name, torch.float32, (None, n_kv_heads * vdim))
+            if t.shape[0] < n_tokens:
+                raise ShapeError(f"sigmoid_attention_prep: {n_tokens} tokens asked of {name}[{t.shape[0]}]")
+    if mix is not None:
+        _need(mix, "mix", torch.float32)
+    _work(0.0, 2.0 * n_tokens * width * proj.element_size())
+    _check(library().bt_sigmoid_attention_prep(
+        _ptr(proj), c_longlong(proj.shape[1]), _ptr(q_weight), _ptr(k_weight), c_float(eps), _ptr(positions),
+        _ptr(token_seq), _ptr(inv_freq), c_int(rot_dims), _ptr(mix), _ptr(v_other), _ptr(v_publish), _ptr(table),
+        c_int(table.shape[1]), c_int(table_len), c_int(PAGE_SIZE), _ptr(pool), c_int(n_tokens), c_int(n_heads),
+        c_int(n_kv_heads), c_int(dim), c_int(vdim), c_int(_code(proj.dtype)), _stream()))
+
+
+def sigmoid_attention(q, out, pool, table, table_len, seq_start, past_len, *, n_seqs, max_new, n_heads, n_kv_heads, dim,
+                      vdim, scale, bias=None, window=0, keep_first=0):
+    """out[t, h] = sum over the positions j that t sees of sigmoid(q[t, h] . k[j, g] * scale + bias[h]) v[j, g], with
+    g = h // (heads / kv_heads): nothing is normalised over the keys.  A token at position i sees j <= i with
+    i - j < window or j < keep_first (`window` 0: every j <= i).  q: rows whose first heads * dim channels are the
+    queries; keys and values: `pool` [pages, kv_heads, PAGE_SIZE, dim + vdim] through `table`; out: [tokens, heads * vdim];
+    scores, sigmoids and sums in 32-bit."""
+    _need(q, "q", (torch.float32, torch.bfloat16))
+    _need(out, "out", q.dtype, (None, n_heads * vdim))
+    _need(pool, "pool", q.dtype, (None, n_kv_heads, PAGE_SIZE, dim + vdim))
+    _need(table, "table", torch.int32)
+    if q.shape[1] < n_heads * dim:
+        raise ShapeError(f"sigmoid_attention: rows of {q.shape[1]} channels hold no {n_heads} queries of {dim}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (n_heads,))
+    if _PROFILE is not None:
+        ctx = float(_PROFILE.context_hint or 0)
+        seen = min(ctx if max_new == 1 else ctx / 2, float(window + keep_first) if window else ctx)
+        rows = n_seqs * max_new
+        _work(2.0 * rows * n_heads * seen * (dim + vdim),
+              (rows * n_heads * (dim + vdim) + n_seqs * min(ctx, seen + max_new) * n_kv_heads * (dim + vdim)) * q.element_size())
+    _check(library().bt_sigmoid_attention(
+        _ptr(q), c_longlong(q.shape[1]), _ptr(pool), _ptr(table), c_int(table.shape[1]), c_int(table_len),
+        c_int(PAGE_SIZE), _ptr(seq_start), _ptr(past_len), _ptr(bias), _ptr(out), c_longlong(out.shape[1]), c_int(n_seqs),
+        c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(dim), c_int(vdim), c_float(scale), c_int(window),
+        c_int(keep_first), c_int(_code(q.dtype)), _stream()))

@@ -203,3 +203,79 @@ class SandwichBlock(Block):
             self.feed_forward.forward(ctx, x, branch)
             kernels.rmsnorm_add(branch, self.norm2b.t_weight, residual, self.norm2b.eps, n_rows=n)
         ctx.ws.release(mark)
+
+
+class OutputNormBlock(Block):
+    """The norm stands on a sublayer's OUTPUT only: x + m * norm1(mixer(x)), then y + m * norm2(feed_forward(y)), with m
+    one number for the whole model.  The sublayers read the stream itself (rounded to the products' type); with a
+    `shift` (parts.token_shift.TokenShift) the mixer reads every row blended with the row of the token before it.
+
+    A sublayer adds into a zeroed 32-bit buffer; one kernel (csrc/rowwise.cu: rmsnorm_add) norms the buffer, adds m
+    times the result to the stream and, where the feed-forward follows, writes the new row in the products' type for
+    it in the same pass.  Both norms are RMS norms of one eps."""
+
+    def __init__(self, mixer: Mixer, norm1: Norm, feed_forward: FeedForward | None = None, norm2: Norm | None = None,
+                 *, scale: float = 1.0, shift=None):
+        if (norm2 is None) != (feed_forward is None):
+            raise ValueError("a block has both a feed-forward and the norm of its output, or neither")
+        norms = [n for n in (norm1, norm2) if n is not None]
+        if any(getattr(n, "has_bias", True) or n.eps != norm1.eps or not hasattr(n, "offset") for n in norms):
+            raise ValueError("the norms of the sublayers' outputs are RMS norms with one eps")
+        self.mixer, self.norm1, self.feed_forward, self.norm2 = mixer, norm1, feed_forward, norm2
+        self.scale, self.shift = float(scale), shift
+
+    def parts(self):
+        found = {"mixer": self.mixer, "norm1": self.norm1}
+        if self.shift is not None:
+            found["shift"] = self.shift
+        if self.feed_forward is not None:
+            found.update({"feed_forward": self.feed_forward, "norm2": self.norm2})
+        return found
+
+    def cache_need(self):
+        need = self.mixer.cache_need()
+        if self.shift is None:
+            return need
+        import dataclasses
+        return dataclasses.replace(need, states=tuple(need.states) + self.shift.states())
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts().values())
+
+    def forward(self, ctx, residual, entry, owns_cache=True):
+        if getattr(ctx, "program", None) is not None:
+            from ..engine.program import ProgramUnsupported
+            raise ProgramUnsupported("a norm on a sublayer's output has no phase in the fused step")
+        n, width = ctx.n_tokens, residual.shape[1]
+        exact = ctx.dtype == torch.float32
+        mark = ctx.ws.mark()
+        branch = ctx.ws.take((n, width), torch.float32)
+        rows = ctx.ws.take((n, width), ctx.dtype) if (self.shift is not None or not exact) else None
+        if self.shift is not None:
+            self.shift.forward(ctx, residual, rows, entry)
+            x = rows
+        elif exact:
+            x = residual
+        else:
+            rows[:n].copy_(residual[:n])
+            x = rows
+        inner = ctx.ws.mark()
+        branch.zero_()
+        self.mixer.forward(ctx, x, branch, entry, owns_cache)
+        ctx.ws.release(inner)
+        if self.feed_forward is None:
+            kernels.rmsnorm_add(branch, self.norm1.t_weight, residual, self.norm1.eps, n_rows=n, factor=self.scale)
+            ctx.ws.release(mark)
+            return
+        # the feed-forward reads the new rows of the stream: as they are in 32-bit, else rounded by the same kernel
+        kernels.rmsnorm_add(branch, self.norm1.t_weight, residual, self.norm1.eps, n_rows=n, factor=self.scale,
+                            next_out=None if exact else rows)
+        x = residual if exact else rows
+        branch.zero_()
+        if getattr(self.feed_forward, "wants_x32", False):
+            self.feed_forward.forward(ctx, x, branch, x32=residual)
+        else:
+            self.feed_forward.forward(ctx, x, branch)
+        kernels.rmsnorm_add(branch, self.norm2.t_weight, residual, self.norm2.eps, n_rows=n, factor=self.scale)
+        ctx.ws.release(mark)

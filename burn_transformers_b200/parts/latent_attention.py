@@ -32,7 +32,13 @@ class LatentAttention(Mixer):
     of latents.  A layer built with `owns_latent=False` has no W_dkv; the model's run order gives it another layer's
     cache entry, whose rows it reads with its own W_uk, W_uv, queries and everything else.
 
-    Tensors (stored [out, in]): `in.weight` = rows of W_q, then W_g, then (owner only) W_dkv; `uk.weight`
+    By argument: `gate=False` leaves the output gate out; `window` = W lets position i see j with 0 <= i - j < W only;
+    `q_rank` = r sends the queries through a latent of their own, c_q = (W_dq h) / rms(W_dq h) * q_norm, q = W_uq c_q
+    (then `in.weight` opens with W_dq's r rows in W_q's place, and the part has `q_norm.weight` [r] and `uq.weight`
+    [heads * (dim + rot_dim), r]).  A windowed layer keeps every position in its pages all the same: the kernels skip
+    the tiles of keys before a block's first visible one.
+
+    Tensors (stored [out, in]): `in.weight` = rows of W_q (or W_dq), then W_g, then (owner only) W_dkv; `uk.weight`
     [heads * dim, kv_rank]; `uv.weight` [heads * vdim, kv_rank]; `latent_norm.weight` [kv_rank] (owner only); `sink`
     [heads] (if `sink`); `out.weight` [width, heads * vdim].
     """
@@ -49,7 +55,8 @@ class LatentAttention(Mixer):
 
     def __init__(self, width: int, n_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float, eps: float,
                  positions, *, owns_latent: bool = True, sink: bool = True, init_std: float = 0.02,
-                 out_init_std: float | None = None):
+                 out_init_std: float | None = None, gate: bool = True, window: int | None = None,
+                 q_rank: int | None = None):
         if min(width, n_heads, dim, vdim, kv_rank) <= 0 or rot_dim < 0:
             raise ShapeError("latent attention: sizes must be positive")
         if kv_rank > 512:
@@ -58,11 +65,16 @@ class LatentAttention(Mixer):
             raise ShapeError("latent attention: needs a rotating position encoding over at most rot_dim channels")
         self.width, self.n_heads, self.dim, self.rot_dim, self.vdim, self.kv_rank = width, n_heads, dim, rot_dim, vdim, kv_rank
         self.scale, self.eps, self.positions = float(scale), float(eps), positions
-        self.owns_latent, self.has_sink = owns_latent, sink
+        if (window is not None and window <= 0) or (q_rank is not None and q_rank <= 0):
+            raise ShapeError("latent attention: a window and a query latent are positive")
+        self.owns_latent, self.has_sink, self.has_gate = owns_latent, sink, gate
+        self.window, self.q_rank = window, q_rank
         self.q_width = n_heads * (dim + rot_dim)
-        self.gate_width = n_heads * vdim
+        self.mixed_width = n_heads * vdim
+        self.gate_width = self.mixed_width if gate else 0
         self.latent_width = kv_rank + rot_dim
-        self.in_width = self.q_width + self.gate_width + (self.latent_width if owns_latent else 0)
+        self.q_in_width = self.q_width if q_rank is None else q_rank      # what the first product gives of the queries
+        self.in_width = self.q_in_width + self.gate_width + (self.latent_width if owns_latent else 0)
         self.init_std = init_std
         self.out_init_std = init_std if out_init_std is None else out_init_std
 
@@ -76,6 +88,9 @@ class LatentAttention(Mixer):
             specs["latent_norm.weight"] = TensorSpec((self.kv_rank,), VECTOR, ("ones",))
         if self.has_sink:
             specs["sink"] = TensorSpec((self.n_heads,), VECTOR, ("normal", 1.0))
+        if self.q_rank is not None:
+            specs["q_norm.weight"] = TensorSpec((self.q_rank,), VECTOR, ("ones",))
+            specs["uq.weight"] = TensorSpec((self.q_width, self.q_rank), MATRIX, ("normal", self.q_rank ** -0.5))
         return specs
 
     def bind(self, tensors):
@@ -98,7 +113,8 @@ class LatentAttention(Mixer):
         hb = min(self.n_heads, rows_per_block)
         tiles = -(-self.n_heads // hb) * -(-ctx.max_new // max(1, rows_per_block // hb)) * ctx.n_seqs
         by_fill = -(-2 * _sm_count(ctx.ws.device) // max(1, tiles))
-        return int(max(1, min(by_fill, -(-ctx.ctx_bound // 32), 64)))
+        span = ctx.ctx_bound if self.window is None else min(ctx.ctx_bound, self.window + 64)
+        return int(max(1, min(by_fill, -(-span // 32), 64)))
 
     def forward(self, ctx, x, residual, entry, owns_cache=True):
         if getattr(ctx, "program", None) is not None:
@@ -112,6 +128,16 @@ class LatentAttention(Mixer):
         rank, rot, dk = self.kv_rank, self.rot_dim, self.latent_width
         proj = ctx.ws.take((n, self.in_width), dtype)
         linear(ctx, x, self.t_in_weight, None, proj, m=n, w_is_nk=True)
+        window = self.window or 0
+        gate_off, latent_off = self.q_in_width, self.q_in_width + self.gate_width
+        if self.q_rank is None:
+            queries = proj
+        else:
+            # the queries out of their own latent: norm of the first q_rank channels, then W_uq
+            low = ctx.ws.take((n, self.q_rank), dtype)
+            kernels.rmsnorm(proj[:, :self.q_rank], self.t_q_norm_weight, low, self.eps, n_rows=n)
+            queries = ctx.ws.take((n, self.q_width), dtype)
+            linear(ctx, low, self.t_uq_weight, None, queries, m=n, w_is_nk=True)
         k_pool, _, group, g = ctx.cache.layer_pools(entry)
         if group.spec.head_dim != dk or group.spec.n_kv_heads != 1:
             raise ShapeError(f"latent attention: the cache entry holds rows of {group.spec.n_kv_heads} x "
@@ -119,7 +145,7 @@ class LatentAttention(Mixer):
         pool = k_pool.view(-1, PAGE_SIZE, dk)
         table = ctx.tables[g]
         freq = self.positions.inv_freq(proj.device)
-        if n <= self.fused_up_to:
+        if n <= self.fused_up_to and self.q_rank is None and self.has_gate:
             # few tokens: query into the latent space + rotation + filing in one launch, the attention, then
             # join of the splits + W_uv + gate in one launch
             q_latent = ctx.ws.take((n, heads * dk), dtype)
@@ -135,7 +161,7 @@ class LatentAttention(Mixer):
             kernels.latent_attention(q_latent, mixed_latent, pool, table, group.table_len, ctx.seq_start, ctx.past_len,
                                      n_tokens=n, n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=heads, rank=rank, rot=rot,
                                      scale=self.scale, sink=self.t_sink if self.has_sink else None, n_splits=splits,
-                                     scratch=scratch, merge=False)
+                                     scratch=scratch, merge=False, window=window)
             mixed = ctx.ws.take((n, self.gate_width), dtype)
             kernels.latent_decode_finish(self.uv_heads, mixed, n_tokens=n, n_splits=splits, scratch=scratch,
                                          mixed_latent=mixed_latent,
@@ -144,17 +170,17 @@ class LatentAttention(Mixer):
             ctx.ws.release(mark)
             return
         if self.owns_latent:
-            kernels.latent_append(proj[:, self.q_width + self.gate_width:], self.t_latent_norm_weight, self.eps,
+            kernels.latent_append(proj[:, latent_off:], self.t_latent_norm_weight, self.eps,
                                   ctx.positions, ctx.token_seq, freq, self.positions.dims, table, group.table_len, pool,
                                   n, rank, rot)
-        q_heads = proj[:, :self.q_width].view(n, heads, self.dim + rot)
-        gate = proj[:, self.q_width:self.q_width + self.gate_width].view(n, heads, self.vdim)
+        q_heads = queries[:, :self.q_width].view(n, heads, self.dim + rot)
+        gate = proj[:, gate_off:latent_off].view(n, heads, self.vdim) if self.has_gate else None
         if dtype == torch.bfloat16 and ctx.fresh and not ctx.is_decode and ctx.max_new >= self.plain_from:
             # fresh prompts: the step's own latent rows, keys and values per head, ordinary attention
             rows = ctx.ws.take((n, dk), dtype)
             keys = ctx.ws.take((n, heads, self.dim + rot), dtype)
             values = ctx.ws.take((n, heads, self.vdim), dtype)
-            mixed = ctx.ws.take((n, self.gate_width), dtype)
+            mixed = ctx.ws.take((n, self.mixed_width), dtype)
             mixed_heads = mixed.view(n, heads, self.vdim)
             if kernels.sink_attention_supports(q_heads, keys, values, gate, mixed_heads):
                 kernels.latent_gather(pool, ctx.positions, ctx.token_seq, table, group.table_len, rows, n_tokens=n)
@@ -167,7 +193,7 @@ class LatentAttention(Mixer):
                     self.positions.rotate_vectors(ctx, q_heads[:, :, self.dim:], q_heads[:, :, self.dim:])
                 kernels.sink_attention(q_heads, keys, values, mixed_heads, ctx.seq_start, n_seqs=ctx.n_seqs,
                                        max_new=ctx.max_new, scale=self.scale,
-                                       sink=self.t_sink if self.has_sink else None, gate=gate)
+                                       sink=self.t_sink if self.has_sink else None, gate=gate, window=window)
                 linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)
                 ctx.ws.release(mark)
                 return
@@ -185,9 +211,9 @@ class LatentAttention(Mixer):
         kernels.latent_attention(q_latent, mixed_latent, pool, table, group.table_len, ctx.seq_start, ctx.past_len,
                                  n_tokens=n, n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=heads, rank=rank, rot=rot,
                                  scale=self.scale, sink=self.t_sink if self.has_sink else None, n_splits=splits,
-                                 scratch=scratch)
+                                 scratch=scratch, window=window)
         # values: W_uv on the weighted latents, times the output gate
-        mixed = ctx.ws.take((n, self.gate_width), dtype)
+        mixed = ctx.ws.take((n, self.mixed_width), dtype)
         kernels.head_linear(mixed_latent.view(n, heads, rank), self.uv_heads, mixed.view(n, heads, self.vdim), n_tokens=n,
                             gate=gate)
         linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)

@@ -1,6 +1,8 @@
 """Position encodings."""
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .. import kernels
@@ -31,14 +33,40 @@ class InterleavedRotary(PositionEncoding):
     """Turns channel pairs of query and key vectors by an angle that grows with the position: the pair (2i, 2i+1),
     i < dims/2, of a vector at position p becomes (u cos a - v sin a, v cos a + u sin a) with a = p * base^(-2i/dims);
     channels from `dims` on pass unchanged.  The frequencies are formed in 64-bit on the host and rounded once; angle,
-    sine and cosine are 32-bit on the device.  Owns no tensor."""
+    sine and cosine are 32-bit on the device.  Owns no tensor.
+
+    `stretch` = (factor, low, high, original) slows the long waves down: with the wavelength l = 2 pi / f of a
+    frequency f, f stays where l < original / high, becomes f / factor where l > original / low, and in between is
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
     rotates = True
 
-    def __init__(self, dims: int, base: float):
+    def __init__(self, dims: int, base: float, stretch: tuple[float, float, float, float] | None = None):
         if dims < 0 or dims % 2:
             raise ValueError(f"a rotation takes an even number of channels, not {dims}")
         self.dims, self.base = int(dims), float(base)
+        self.stretch = None if stretch is None else tuple(float(v) for v in stretch)
+        if self.stretch is not None and (len(self.stretch) != 4 or self.stretch[0] <= 0 or self.stretch[3] <= 0
+                                         or self.stretch[2] <= self.stretch[1]):
+            raise ValueError(f"a stretch is (factor > 0, low, high > low, original > 0), not {stretch}")
         self._freq: dict = {}
+
+    def frequencies(self) -> list[float]:
+        """The dims / 2 frequencies, in 64-bit."""
+        values = [self.base ** (-2.0 * i / self.dims) for i in range(self.dims // 2)]
+        if self.stretch is None:
+            return values
+        factor, low, high, original = self.stretch
+        out = []
+        for f in values:
+            wavelength = 2.0 * math.pi / f
+            if wavelength < original / high:
+                out.append(f)
+            elif wavelength > original / low:
+                out.append(f / factor)
+            else:
+                s = (original / wavelength - low) / (high - low)
+                out.append((1.0 - s) * f / factor + s * f)
+        return out
 
     def inv_freq(self, device) -> torch.Tensor:
         """[dims / 2] 32-bit frequencies on `device` (made once per device; before any stream capture: a mixer that
@@ -46,8 +74,7 @@ class InterleavedRotary(PositionEncoding):
         device = torch.device(device)
         hit = self._freq.get(device)
         if hit is None:
-            half = max(1, self.dims // 2)
-            values = [self.base ** (-2.0 * i / self.dims) if self.dims else 1.0 for i in range(half)]
+            values = self.frequencies() or [1.0]
             hit = torch.tensor(values, dtype=torch.float64).to(torch.float32).to(device)
             self._freq[device] = hit
         return hit
