@@ -1,7 +1,7 @@
 """Decode and prefill throughput of GPT-2 (random weights, synthetic tokens) on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--points all|small] [--profile]
-    python bench.py --arch sovozen|gokezen|rakarax [--sizes small,medium]
+    python bench.py --arch sovozen|gokezen|rakarax|bosalix [--sizes small,medium]
 
 A step is one decode step of a batch of 8 sequences of GPT-2 small.  The run prints one JSON line: `value` is decoded
 tokens per second, timed on the device with CUDA events over exactly K steps; `e2e` is the same through the public
@@ -419,14 +419,36 @@ def rakarax(size: str) -> dict:
             "layers": layers}
 
 
+def bosalix(size: str) -> dict:
+    """A Bosalix with as many layers, the width and the heads of GPT-2 `size`: in turn a sigmoid attention (a key head for
+    every four query heads, window 512 with 4 kept first positions, half of each head rotated, values mixed with the
+    first layer's) and a windowed latent attention (latent 256 or 512 + 32 or 64 rotated, queries through a latent of
+    half the width); every layer with routed experts without a gate (16 and 2 that hand their input on, 4 a token), the
+    weights a token uses equal to GPT-2's (4 x 2 x ff x width = 8 x width^2)."""
+    n_layer, width, heads = {"small": (12, 768, 12), "medium": (24, 1024, 16)}[size]
+    rank, rot = {"small": (256, 32), "medium": (512, 64)}[size]
+    dim = 64
+    mlp = {"kind": "moe", "expert": {"ff": width}, "router": {"experts": 16, "identity": 2, "top": 4}}
+    sigmoid = {"type": "attention", "mlp": mlp,
+               "mixer": {"heads": heads, "kv_heads": heads // 4, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "v_mix": True,
+                         "rot": {"dims": dim // 2, "base": 10000.0,
+                                 "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}},
+                         "mask": {"size": 512, "keep_first": 4}}}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "kv_rank": rank, "q_rank": width // 2,
+                        "scale": (dim + rot) ** -0.5, "rot": {"dims": rot, "base": 10000.0}, "mask": {"size": 512}}}
+    return {"architecture": "Bosalix", "vocab": 50257, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "embedding": {"scale": 1.0}, "layers": [dict(latent) if i % 2 else dict(sigmoid) for i in range(n_layer)]}
+
+
 ARCH_PAIRS = {"sovozen": (sovozen, "gpt2", gpt2), "gokezen": (gokezen, "sovozen", sovozen),
-              "rakarax": (rakarax, "gokezen", gokezen)}
+              "rakarax": (rakarax, "gokezen", gokezen), "bosalix": (bosalix, "gokezen", gokezen)}
 
 
 def run_arch_compare(args):
-    """--arch sovozen | gokezen | rakarax: prefill and decode throughput of that design beside the library's closest
-    other model at the same width and depth (GPT-2 for Sovozen, Sovozen for Gokezen, Gokezen for Rakarax; random weights,
-    bfloat16), and where each
+    """--arch sovozen | gokezen | rakarax | bosalix: prefill and decode throughput of that design beside the library's
+    closest other model at the same width and depth (GPT-2 for Sovozen, Sovozen for Gokezen, Gokezen for Rakarax and for
+    Bosalix; random weights, bfloat16), and where each
     spends a prefill and a decode step, kernel by kernel, against the measured peaks.  One JSON line; the default
     workload of this file is untouched."""
     import numpy as np
@@ -647,10 +669,10 @@ def main() -> int:
     parser.add_argument("--profile", action="store_true",
                         help="print where a prefill and a decode step spend their time, kernel by kernel, instead")
     parser.add_argument("--model", choices=["small", "medium", "xl"], default="small", help="the model --profile looks at")
-    parser.add_argument("--arch", choices=["gpt2", "sovozen", "gokezen", "rakarax"], default="gpt2",
-                        help="sovozen, gokezen, rakarax: measure that design beside the closest other model of equal width and "
+    parser.add_argument("--arch", choices=["gpt2", "sovozen", "gokezen", "rakarax", "bosalix"], default="gpt2",
+                        help="sovozen, gokezen, rakarax, bosalix: measure that design beside the closest other model of equal width and "
                              "depth instead (see --sizes)")
-    parser.add_argument("--sizes", default="small,medium", help="with --arch sovozen | gokezen | rakarax: which widths (small, medium)")
+    parser.add_argument("--sizes", default="small,medium", help="with --arch sovozen | gokezen | rakarax | bosalix: which widths (small, medium)")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate (Cargo.toml only): pip "

@@ -96,7 +96,8 @@ int bt_sink_attention_supports(int dq, int dv, long long q_row, int q_head, long
 int bt_sink_attention(const void* q, long long q_row, int q_head, const void* k, long long k_row, int k_head,
                       const void* v, long long v_row, int v_head, const void* gate, long long gate_row, int gate_head,
                       void* out, long long out_row, int out_head, const int* seq_start, const float* sink, int n_seqs,
-                      int max_new, int n_heads, int dq, int dv, float scale, cudaStream_t stream);
+                      int max_new, int n_heads, int dq, int dv, float scale, int window, int keep_first, int kv_group,
+                      int sigmoid, const float* bias, cudaStream_t stream);
 int bt_head_linear(const void* a, long long a_row_stride, int a_head_stride, const void* w, void* out,
                    long long out_row_stride, int out_head_stride, const void* gate, long long gate_row_stride,
                    int gate_head_stride, int n_tokens, int n_heads, int K, int N, int tensor_cores, int dtype,
@@ -105,10 +106,11 @@ long long bt_latent_attention_scratch_floats(int n_tokens, int n_heads, int rank
 int bt_latent_attention(const void* q, long long q_row_stride, const void* pool, const int* table, int table_stride,
                         int table_len, int page_size, const int* seq_start, const int* past_len, const float* sink,
                         void* out, long long out_row_stride, float* part, int n_tokens, int n_seqs, int max_new,
-                        int n_heads, int rank, int rot, float scale, int n_splits, int tensor_cores, int merge, int dtype,
-                        cudaStream_t stream);
+                        int n_heads, int rank, int rot, float scale, int n_splits, int window, int tensor_cores, int merge,
+                        int dtype, cudaStream_t stream);
 // The steps around the latent attention fused for steps of few tokens (csrc/latent_decode.cu).
-int bt_latent_decode_prep(const void* proj, long long row_stride, int q_off, int latent_off, const void* uk,
+int bt_latent_decode_prep(const void* proj, long long row_stride, int q_off, int latent_off, const void* latent_rows,
+                          long long latent_row_stride, const void* uk,
                           const float* norm_weight, float eps, const int* positions, const int* token_seq,
                           const float* inv_freq, int rot_dims, const int* table, int table_stride, int table_len,
                           int page_size, void* pool, void* q_latent, int n_tokens, int n_heads, int dim, int rank, int rot,
@@ -129,7 +131,20 @@ int bt_rmsnorm(const void* x, int x_dtype, long long x_row_stride, const float* 
                long long gate_row_stride, void* out, int out_dtype, long long out_row_stride, int n_rows, int width,
                int groups, float eps, int gate_rule, cudaStream_t stream);
 int bt_rmsnorm_add(const float* x, const float* weight, float* stream_rows, const float* next_weight, void* next_out,
-                   int next_dtype, long long n_rows, int width, float eps, cudaStream_t stream);
+                   int next_dtype, long long n_rows, int width, float eps, float factor, cudaStream_t stream);
+// The blend of every row with the row of the token before it, with the kept row per sequence (csrc/rowwise.cu).
+int bt_token_shift(const float* x, const float* shift, float* state, const int* slots, const int* seq_start,
+                   const int* token_seq, void* out, int out_dtype, long long n_rows, int width, cudaStream_t stream);
+// Attention whose weights are sigmoids of the scores (csrc/sigmoid_attention.cu).
+int bt_sigmoid_attention_prep(void* proj, long long row_stride, const float* q_weight, const float* k_weight, float eps,
+                              const int* positions, const int* token_seq, const float* inv_freq, int rot_dims,
+                              const float* mix, const float* v_other, float* v_publish, const int* table,
+                              int table_stride, int table_len, int page_size, void* pool, int n_tokens, int n_heads,
+                              int n_kv_heads, int dim, int vdim, int dtype, cudaStream_t stream);
+int bt_sigmoid_attention(const void* q, long long q_row_stride, const void* pool, const int* table, int table_stride,
+                         int table_len, int page_size, const int* seq_start, const int* past_len, const float* bias,
+                         void* out, long long out_row_stride, int n_seqs, int max_new, int n_heads, int n_kv_heads,
+                         int dim, int vdim, float scale, int window, int keep_first, int dtype, cudaStream_t stream);
 int bt_polynorm(const void* x, const float* coef, void* out, long long n_rows, int width, float eps, int dtype,
                 cudaStream_t stream);
 int bt_rotary_half(const void* src, long long src_row_stride, int src_dtype, float* dst, long long dst_row_stride,
@@ -175,7 +190,8 @@ int bt_mlstm_chunked(const void* proj, long long row_stride, int q_off, int k_of
                      long long n_rows, int max_new, int n_seqs, int n_heads, int dim, int vdim, int dtype,
                      cudaStream_t stream);
 int bt_moe_route(const void* x, long long x_row_stride, const void* router, int n_tokens, int K, int E, int top,
-                 int n_groups, int keep, float scale, int* ids, float* weights, int dtype, cudaStream_t stream);
+                 int n_groups, int keep, float scale, int softmax, const float* choice_bias, int normalise, int* ids,
+                 float* weights, int dtype, cudaStream_t stream);
 int bt_moe_tile_rows();
 int bt_moe_sort(const int* ids, int total, int E, int* offsets, int* tile_first, int* order, int* place,
                 cudaStream_t stream);
@@ -183,7 +199,7 @@ int bt_moe_expert(int first, const void* a, long long a_row_stride, const void* 
                   const int* tile_first, const int* order, const float* pair_weight, int pairs, int E, int top, int K,
                   int N, int act, float limit, int tensor_cores, int dtype, cudaStream_t stream);
 int bt_moe_combine(const float* part, const int* place, float* stream_rows, long long n_tokens, int top, int width,
-                   cudaStream_t stream);
+                   const int* ids, const float* weights, const float* input, int n_stored, cudaStream_t stream);
 int bt_add_vector(float* x, const float* vec, long long n_rows, int width, cudaStream_t stream);
 int bt_add_rows(float* x, const float* a, const float* b, const float* c, long long n, cudaStream_t stream);
 

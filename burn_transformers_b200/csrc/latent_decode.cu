@@ -57,7 +57,8 @@ __device__ __forceinline__ void ld_matvec(const float* x, const T* __restrict__ 
 
 template <typename T>
 __global__ void __launch_bounds__(LD_THREADS)
-latent_decode_prep_kernel(const T* __restrict__ proj, long long row_stride, int q_off, int latent_off,
+latent_decode_prep_kernel(const T* __restrict__ proj, long long row_stride, int q_off,
+                          const T* __restrict__ latent_rows, long long latent_row_stride,   // the tokens' [latent | key part]
                           const T* __restrict__ uk,                 // [heads][dim][rank]
                           const float* __restrict__ norm_weight, float eps, const int* __restrict__ positions,
                           const int* __restrict__ token_seq, const float* __restrict__ inv_freq, int rot_dims,
@@ -100,7 +101,7 @@ latent_decode_prep_kernel(const T* __restrict__ proj, long long row_stride, int 
   for (int c = rot_dims + threadIdx.x; c < rot; c += blockDim.x) dst[rank + c] = q[dim + c];
   if (!owns || h != 0) return;
   // the token's own latent row: norm, rotation, page (the same arithmetic as latent_append_kernel)
-  const T* lat = row + latent_off;
+  const T* lat = latent_rows + (long long)t * latent_row_stride;
   float ss = 0.f;
   for (int c = threadIdx.x; c < rank; c += blockDim.x) {
     const float v = to_float(lat[c]);
@@ -191,7 +192,10 @@ latent_decode_finish_kernel(const float* __restrict__ part, const T* __restrict_
 
 }  // namespace bt
 
-extern "C" int bt_latent_decode_prep(const void* proj, long long row_stride, int q_off, int latent_off, const void* uk,
+// The queries are the channels from `q_off` on of `proj`'s rows; the tokens' latent rows are `latent_rows` (rows
+// `latent_row_stride` elements apart), or, when that is null, the channels from `latent_off` on of the same `proj` rows.
+extern "C" int bt_latent_decode_prep(const void* proj, long long row_stride, int q_off, int latent_off,
+                                     const void* latent_rows, long long latent_row_stride, const void* uk,
                                      const float* norm_weight, float eps, const int* positions, const int* token_seq,
                                      const float* inv_freq, int rot_dims, const int* table, int table_stride,
                                      int table_len, int page_size, void* pool, void* q_latent, int n_tokens, int n_heads,
@@ -202,15 +206,22 @@ extern "C" int bt_latent_decode_prep(const void* proj, long long row_stride, int
   if (n_tokens == 0) return 0;
   const dim3 grid(n_tokens, n_heads), block(LD_THREADS);
   const size_t smem = (size_t)dim * sizeof(float);
+  const size_t elem = dtype == kF32 ? 4 : 2;
+  if (latent_rows == nullptr) {
+    latent_rows = (const char*)proj + (size_t)latent_off * elem;
+    latent_row_stride = row_stride;
+  }
   if (dtype == kF32)
     BT_PDL_OK("latent_decode_prep", launch_pdl(latent_decode_prep_kernel<float>, grid, block, smem, stream, 1,
-                                               (const float*)proj, row_stride, q_off, latent_off, (const float*)uk,
+                                               (const float*)proj, row_stride, q_off, (const float*)latent_rows,
+                                               latent_row_stride, (const float*)uk,
                                                norm_weight, eps, positions, token_seq, inv_freq, rot_dims, table,
                                                table_stride, table_len, page_size, (float*)pool, (float*)q_latent, n_heads,
                                                dim, rank, rot, owns));
   else if (dtype == kBF16)
     BT_PDL_OK("latent_decode_prep", launch_pdl(latent_decode_prep_kernel<__nv_bfloat16>, grid, block, smem, stream, 1,
-                                               (const __nv_bfloat16*)proj, row_stride, q_off, latent_off,
+                                               (const __nv_bfloat16*)proj, row_stride, q_off,
+                                               (const __nv_bfloat16*)latent_rows, latent_row_stride,
                                                (const __nv_bfloat16*)uk, norm_weight, eps, positions, token_seq, inv_freq,
                                                rot_dims, table, table_stride, table_len, page_size, (__nv_bfloat16*)pool,
                                                (__nv_bfloat16*)q_latent, n_heads, dim, rank, rot, owns));

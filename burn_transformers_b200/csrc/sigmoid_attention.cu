@@ -5,8 +5,9 @@
 //                           shared by the heads), then its first `rot_dims` channels are turned by the token's
 //                           position, channel i paired with channel i + rot_dims / 2; every value head is divided by its
 //                           root mean square (no weight) and may be mixed with another layer's values of the same token,
-//                           v <- (1 - lambda) v + lambda v_other.  Queries are rewritten in place; key and value go into
-//                           the token's row of the layer's pages, [key | value] per position and key head.
+//                           v <- (1 - lambda) v + lambda v_other.  All three are rewritten in place (a step of fresh prompts
+//                           attends over its own rows); key and value also go into the token's row of the layer's pages,
+//                           [key | value] per position and key head.
 //   sigmoid_attention       out[t, h] = sum over the visible positions j of sigmoid(q[t, h] . k[j, g] * scale + bias[h])
 //                           v[j, g], g = h / (heads / kv_heads); position i sees j <= i with i - j < window or
 //                           j < keep_first (window 0: every j <= i).  A block holds a tile of tokens with all query heads
@@ -46,8 +47,8 @@ sigmoid_attention_prep_kernel(T* __restrict__ proj, long long row_stride, const 
       const bool is_q = unit < n_heads;
       T* src = row + (long long)unit * dim;
       const float* w = is_q ? q_weight : k_weight;
-      T* dst = is_q ? src
-                    : pool + (((page * n_kv_heads + (unit - n_heads)) * page_size) + (pos - lp * page_size)) * dkv;
+      T* cell = is_q ? nullptr
+                     : pool + (((page * n_kv_heads + (unit - n_heads)) * page_size) + (pos - lp * page_size)) * dkv;
       float ss = 0.f;
       for (int c = lane; c < dim; c += 32) {
         const float v = to_float(src[c]);
@@ -58,13 +59,19 @@ sigmoid_attention_prep_kernel(T* __restrict__ proj, long long row_stride, const 
         const float u = to_float(src[i]) * inv * w[i], v = to_float(src[i + half]) * inv * w[i + half];
         float sn, cs;
         sincosf(fpos * inv_freq[i], &sn, &cs);
-        dst[i] = from_float<T>(u * cs - v * sn);
-        dst[i + half] = from_float<T>(v * cs + u * sn);
+        const T a = from_float<T>(u * cs - v * sn), b = from_float<T>(v * cs + u * sn);
+        src[i] = a;
+        src[i + half] = b;
+        if (cell != nullptr) { cell[i] = a; cell[i + half] = b; }
       }
-      for (int c = 2 * half + lane; c < dim; c += 32) dst[c] = from_float<T>(to_float(src[c]) * inv * w[c]);
+      for (int c = 2 * half + lane; c < dim; c += 32) {
+        const T a = from_float<T>(to_float(src[c]) * inv * w[c]);
+        src[c] = a;
+        if (cell != nullptr) cell[c] = a;
+      }
     } else {
       const int g = unit - n_heads - n_kv_heads;
-      const T* src = row + (long long)(n_heads + n_kv_heads) * dim + (long long)g * vdim;
+      T* src = row + (long long)(n_heads + n_kv_heads) * dim + (long long)g * vdim;
       T* dst = pool + (((page * n_kv_heads + g) * page_size) + (pos - lp * page_size)) * dkv + dim;
       float ss = 0.f;
       for (int c = lane; c < vdim; c += 32) {
@@ -78,6 +85,7 @@ sigmoid_attention_prep_kernel(T* __restrict__ proj, long long row_stride, const 
         if (v_other != nullptr) v = (1.f - lambda) * v + lambda * v_other[at + c];
         if (v_publish != nullptr) v_publish[at + c] = v;
         dst[c] = from_float<T>(v);
+        src[c] = from_float<T>(v);
       }
     }
   }
@@ -193,6 +201,157 @@ sigmoid_attention_kernel(const T* __restrict__ q, long long q_row_stride, const 
   }
 }
 
+// Steps of one token a sequence.  grid: (key heads x head tiles, sequences); a block holds up to SD_ROWS query heads of
+// one key head, and its W warps share the KEYS: warp w takes the visible key tiles w, w + W, ... (first those that hold
+// kept first positions and lie before the window, then the window's), each into shared memory of its own, so no block
+// barrier stands between tiles.  For the scores a lane is a key and holds all rows' scores; for the value sum a lane
+// is a set of value channels.  The warps' partial sums meet in shared memory and are added in warp order: which warp
+// takes which tile depends on the token's position and the window only, so the sum's order does not depend on what
+// else the step holds.
+constexpr int SD_ROWS = 8;
+
+template <typename T, int DVL>
+__global__ void __launch_bounds__(256)
+sigmoid_attention_decode_kernel(const T* __restrict__ q, long long q_row_stride, const T* __restrict__ pool,
+                                const int* __restrict__ table, int table_stride, int table_len, int page_size,
+                                const int* __restrict__ seq_start, const int* __restrict__ past_len,
+                                const float* __restrict__ bias, T* __restrict__ out, long long out_row_stride,
+                                int n_heads, int n_kv_heads, int head_tiles, int dim, int vdim, float scale, int window,
+                                int keep_first) {
+  extern __shared__ float smem[];
+  const int n_warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ks = dim + 1, dkv = dim + vdim;
+  float* q_s = smem;                                              // [SD_ROWS][dim]
+  float* k_s = q_s + SD_ROWS * dim + (size_t)warp * SG_TK * (ks + vdim);   // this warp's [SG_TK][ks]
+  float* v_s = k_s + SG_TK * ks;                                  // this warp's [SG_TK][vdim]
+  pdl_trigger();
+  pdl_wait();
+  const int seq = blockIdx.y, g = blockIdx.x / head_tiles, head_tile = blockIdx.x - g * head_tiles;
+  const int group_heads = n_heads / n_kv_heads;
+  const int h0 = g * group_heads + head_tile * SD_ROWS;
+  const int rows = min(SD_ROWS, (g + 1) * group_heads - h0);
+  const long long token = seq_start[seq];
+  const int pos = past_len[seq];
+  for (int i = threadIdx.x; i < SD_ROWS * dim; i += blockDim.x) {
+    const int r = i / dim, d = i - r * dim;
+    q_s[i] = r < rows ? to_float(q[token * q_row_stride + (long long)(h0 + r) * dim + d]) : 0.f;
+  }
+  __syncthreads();
+  float row_bias[SD_ROWS], acc[SD_ROWS][DVL];
+#pragma unroll
+  for (int r = 0; r < SD_ROWS; ++r) {
+    row_bias[r] = r < rows && bias != nullptr ? bias[h0 + r] : 0.f;
+#pragma unroll
+    for (int j = 0; j < DVL; ++j) acc[r][j] = 0.f;
+  }
+  const int n_tiles = pos / SG_TK + 1;
+  const int window_tile = window > 0 ? max(0, pos - window + 1) / SG_TK : 0;
+  const int kept_only = window > 0 ? min((min(keep_first, pos + 1) + SG_TK - 1) / SG_TK, window_tile) : 0;
+  const int n_visible = kept_only + n_tiles - window_tile;
+  for (int idx = warp; idx < n_visible; idx += n_warps) {
+    const int tile = idx < kept_only ? idx : window_tile + (idx - kept_only);
+    const int j0 = tile * SG_TK;
+    __syncwarp();          // the lanes are done with the tile before
+    for (int kk = 0; kk < SG_TK; ++kk) {
+      const int j = j0 + kk;
+      if (j <= pos) {
+        const int lp = j / page_size;
+        const long long page = table[(long long)seq * table_stride + (lp % table_len)];
+        const T* src = pool + (((page * n_kv_heads + g) * page_size) + (j - lp * page_size)) * dkv;
+        for (int d = lane; d < dkv; d += 32) {
+          const float v = to_float(src[d]);
+          if (d < dim) k_s[kk * ks + d] = v; else v_s[kk * vdim + d - dim] = v;
+        }
+      } else {
+        for (int d = lane; d < dkv; d += 32)
+          if (d < dim) k_s[kk * ks + d] = 0.f; else v_s[kk * vdim + d - dim] = 0.f;
+      }
+    }
+    __syncwarp();
+    float s[SD_ROWS];
+#pragma unroll
+    for (int r = 0; r < SD_ROWS; ++r) s[r] = 0.f;
+    const float* krow = k_s + lane * ks;
+    for (int d = 0; d < dim; ++d) {
+      const float kv = krow[d];
+#pragma unroll
+      for (int r = 0; r < SD_ROWS; ++r) s[r] = fmaf(q_s[r * dim + d], kv, s[r]);
+    }
+    const int j = j0 + lane, gap = pos - j;
+    const bool seen = gap >= 0 && (window <= 0 || gap < window || j < keep_first);
+#pragma unroll
+    for (int r = 0; r < SD_ROWS; ++r) s[r] = seen ? 1.f / (1.f + expf(-(s[r] * scale + row_bias[r]))) : 0.f;
+    for (int kk = 0; kk < SG_TK; ++kk) {
+      float pk[SD_ROWS];
+#pragma unroll
+      for (int r = 0; r < SD_ROWS; ++r) pk[r] = __shfl_sync(0xffffffffu, s[r], kk);
+#pragma unroll
+      for (int jj = 0; jj < DVL; ++jj) {
+        const int c = lane + 32 * jj;
+        const float v = c < vdim ? v_s[kk * vdim + c] : 0.f;
+#pragma unroll
+        for (int r = 0; r < SD_ROWS; ++r) acc[r][jj] = fmaf(pk[r], v, acc[r][jj]);
+      }
+    }
+  }
+  // the warps' sums, added in warp order (the tiles' shared memory is free now)
+  __syncthreads();
+  float* sums = q_s + SD_ROWS * dim;                              // [n_warps][SD_ROWS][vdim]
+#pragma unroll
+  for (int r = 0; r < SD_ROWS; ++r)
+#pragma unroll
+    for (int jj = 0; jj < DVL; ++jj) {
+      const int c = lane + 32 * jj;
+      if (c < vdim) sums[((size_t)warp * SD_ROWS + r) * vdim + c] = acc[r][jj];
+    }
+  __syncthreads();
+  for (int i = threadIdx.x; i < rows * vdim; i += blockDim.x) {
+    const int r = i / vdim, c = i - r * vdim;
+    float total = 0.f;
+    for (int w = 0; w < n_warps; ++w) total += sums[((size_t)w * SD_ROWS + r) * vdim + c];
+    out[token * out_row_stride + (long long)(h0 + r) * vdim + c] = from_float<T>(total);
+  }
+}
+
+template <typename T>
+static int launch_sigmoid_attention_decode(const T* q, long long q_row_stride, const T* pool, const int* table,
+                                           int table_stride, int table_len, int page_size, const int* seq_start,
+                                           const int* past_len, const float* bias, T* out, long long out_row_stride,
+                                           int n_seqs, int n_heads, int n_kv_heads, int dim, int vdim, float scale,
+                                           int window, int keep_first, cudaStream_t stream) {
+  const int group_heads = n_heads / n_kv_heads;
+  const int head_tiles = (group_heads + SD_ROWS - 1) / SD_ROWS;
+  const int dvl = (vdim + 31) / 32;
+  // as many warps as their key and value tiles fit into shared memory (the sums reuse the tiles' place: smaller)
+  int warps = 8;
+  auto bytes = [&](int w) { return ((size_t)SD_ROWS * dim + (size_t)w * SG_TK * (dim + 1 + vdim)) * sizeof(float); };
+  while (warps > 1 && bytes(warps) > 160 * 1024) warps >>= 1;
+  const size_t smem = bytes(warps);
+  BT_CHECK(smem <= 200 * 1024, "sigmoid_attention: heads of %d + %d channels need %zu bytes of shared memory", dim, vdim,
+           smem);
+  BT_CHECK(n_kv_heads * head_tiles <= 65535 * 32 && n_seqs <= 65535, "sigmoid_attention: bad sizes kv_heads=%d seqs=%d",
+           n_kv_heads, n_seqs);
+  const dim3 grid(n_kv_heads * head_tiles, n_seqs), block(warps * 32);
+#define BT_SD(DVL)                                                                                                     \
+  do {                                                                                                                 \
+    auto kernel = sigmoid_attention_decode_kernel<T, DVL>;                                                             \
+    if (smem > 48 * 1024) {                                                                                            \
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+      BT_CHECK(e == cudaSuccess, "sigmoid_attention: cannot reserve %zu bytes of shared memory", smem);                \
+    }                                                                                                                  \
+    BT_PDL_OK("sigmoid_attention_decode",                                                                              \
+              launch_pdl(kernel, grid, block, smem, stream, 1, q, q_row_stride, pool, table, table_stride, table_len,  \
+                         page_size, seq_start, past_len, bias, out, out_row_stride, n_heads, n_kv_heads, head_tiles,   \
+                         dim, vdim, scale, window, keep_first));                                                       \
+  } while (0)
+  if (dvl <= 1) BT_SD(1);
+  else if (dvl <= 2) BT_SD(2);
+  else if (dvl <= 4) BT_SD(4);
+  else BT_SD(8);
+#undef BT_SD
+  return 0;
+}
+
 template <typename T>
 static int launch_sigmoid_attention(const T* q, long long q_row_stride, const T* pool, const int* table, int table_stride,
                                     int table_len, int page_size, const int* seq_start, const int* past_len,
@@ -277,6 +436,15 @@ extern "C" int bt_sigmoid_attention(const void* q, long long q_row_stride, const
            "sigmoid_attention: bad sizes heads=%d kv_heads=%d dim=%d vdim=%d (up to 256) window=%d keep_first=%d", n_heads,
            n_kv_heads, dim, vdim, window, keep_first);
   if (n_seqs == 0 || max_new == 0) return 0;
+  if (max_new == 1 && dtype == kF32)
+    return launch_sigmoid_attention_decode((const float*)q, q_row_stride, (const float*)pool, table, table_stride,
+                                           table_len, page_size, seq_start, past_len, bias, (float*)out, out_row_stride,
+                                           n_seqs, n_heads, n_kv_heads, dim, vdim, scale, window, keep_first, stream);
+  if (max_new == 1 && dtype == kBF16)
+    return launch_sigmoid_attention_decode((const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)pool, table,
+                                           table_stride, table_len, page_size, seq_start, past_len, bias,
+                                           (__nv_bfloat16*)out, out_row_stride, n_seqs, n_heads, n_kv_heads, dim, vdim,
+                                           scale, window, keep_first, stream);
   if (dtype == kF32)
     return launch_sigmoid_attention((const float*)q, q_row_stride, (const float*)pool, table, table_stride, table_len,
                                     page_size, seq_start, past_len, bias, (float*)out, out_row_stride, n_seqs, max_new,

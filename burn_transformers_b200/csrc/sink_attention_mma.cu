@@ -34,10 +34,14 @@ struct SinkAttentionArgs {
   int dq, dv;
   float scale;
   int window;      // > 0: a row sees the last `window` positions up to its own
+  int keep_first;  // with a window: positions below this stay visible to every later row
+  int kv_group;    // query heads that share a key and value head (1: every head has its own)
+  const float* bias;   // SIGMOID: a number per head added to the scaled score
 };
 
-// VCT: the most value channels (a multiple of 16)
-template <int VCT>
+// VCT: the most value channels (a multiple of 16).  SIGMOID: the weight of a visible key is sigmoid(score * scale + bias[head])
+// and nothing is normalised over the keys (no running maximum, no denominator, no sink).
+template <int VCT, bool SIGMOID>
 __global__ void __launch_bounds__(128) sink_attention_mma_kernel(SinkAttentionArgs p) {
   extern __shared__ __align__(16) unsigned char sa_smem[];
   constexpr int NP = VCT / 16;
@@ -73,6 +77,7 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(SinkAttentionAr
   const int last = t0 + n_valid - 1;                 // the last key any row of the block sees
   const int n_tiles = last / SA_KT + 1;
   const int kq = p.dq / 8, kv = p.dv / 8;
+  const int kv_head = head / p.kv_group;
   auto load_tile = [&](int kt, int buf) {
     const int j0 = kt * SA_KT;
     __nv_bfloat16* kd = k_s + buf * SA_KT * ldq;
@@ -83,17 +88,25 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(SinkAttentionAr
       const bool ok = j <= last;
       const long long tok = first + (ok ? j : 0);
       if (c < kq)
-        sa_cp_async16(ds_smem(kd + kk * ldq + c * 8), p.k + tok * p.k_row + (long long)head * p.k_head + c * 8, ok ? 16 : 0);
+        sa_cp_async16(ds_smem(kd + kk * ldq + c * 8), p.k + tok * p.k_row + (long long)kv_head * p.k_head + c * 8, ok ? 16 : 0);
       else
-        sa_cp_async16(ds_smem(vd + kk * ldv + (c - kq) * 8), p.v + tok * p.v_row + (long long)head * p.v_head + (c - kq) * 8,
+        sa_cp_async16(ds_smem(vd + kk * ldv + (c - kq) * 8), p.v + tok * p.v_row + (long long)kv_head * p.v_head + (c - kq) * 8,
                       ok ? 16 : 0);
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
-  const int kt_first = p.window > 0 ? max(0, t0 - p.window + 1) / SA_KT : 0;      // tiles before it: outside every row's window
-  load_tile(kt_first, kt_first & 1);
+  // tiles before kt_first lie outside every row's window; those that hold kept first positions are walked all the same
+  const int kt_first = p.window > 0 ? max(0, t0 - p.window + 1) / SA_KT : 0;
+  const int kept_tiles = p.window > 0 ? (min(p.keep_first, last + 1) + SA_KT - 1) / SA_KT : 0;
+  auto next_tile = [&](int kt) {
+    const int n = kt + 1;
+    return (n >= kept_tiles && n < kt_first) ? kt_first : n;
+  };
+  const int kt_begin = kept_tiles > 0 ? 0 : kt_first;
+  load_tile(kt_begin, 0);
   float m_run[2], l_run[2];
-  const bool has_sink = p.sink != nullptr;
+  const bool has_sink = !SIGMOID && p.sink != nullptr;
+  const float bias_log2 = SIGMOID && p.bias != nullptr ? p.bias[head] * LOG2E : 0.f;
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
     m_run[e] = has_sink ? p.sink[head] * LOG2E : -INFINITY;
@@ -108,11 +121,11 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(SinkAttentionAr
   const int row0 = t0 + warp * 16 + g;               // this lane's rows: row0 and row0 + 8 (positions inside the sequence)
   const unsigned q_addr = ds_smem(q_s + (warp * 16 + (lane & 15)) * ldq + (lane >> 4) * 8);
   const int blk = lane >> 3;
-  for (int kt = kt_first; kt < n_tiles; ++kt) {
-    const int buf = kt & 1;
+  for (int kt = kt_begin, round = 0; kt < n_tiles; kt = next_tile(kt), ++round) {
+    const int buf = round & 1;
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();
-    if (kt + 1 < n_tiles) load_tile(kt + 1, buf ^ 1);
+    if (next_tile(kt) < n_tiles) load_tile(next_tile(kt), buf ^ 1);
     const int j0 = kt * SA_KT;
     if (!active || j0 > t0 + warp * 16 + 15) continue;      // (no row of this warp sees the tile)
     const __nv_bfloat16* ktile = k_s + buf * SA_KT * ldq;
@@ -142,10 +155,22 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(SinkAttentionAr
         const int j = j0 + n * 8 + qd * 2 + (e & 1);
         const int rr = e >> 1;
         const int row = row0 + 8 * rr;
-        const float val = (row < n_new && j <= row && (p.window <= 0 || row - j < p.window)) ? s[n][e] * scale_log2 : -INFINITY;
+        const bool seen = row < n_new && j <= row && (p.window <= 0 || row - j < p.window || j < p.keep_first);
+        const float val = seen ? s[n][e] * scale_log2 : -INFINITY;
         s[n][e] = val;
         mx[rr] = fmaxf(mx[rr], val);
       }
+    unsigned pa[SA_KT / 16][4];                               // the weights as the value product's first operand, per 16 keys
+    if (SIGMOID) {
+#pragma unroll
+      for (int n = 0; n < SA_NT; ++n) {
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) pv[e] = s[n][e] == -INFINITY ? 0.f : 1.f / (1.f + ds_exp2(-(s[n][e] + bias_log2)));
+        pa[n >> 1][(n & 1) * 2] = ds_pack(pv[0], pv[1]);
+        pa[n >> 1][(n & 1) * 2 + 1] = ds_pack(pv[2], pv[3]);
+      }
+    } else {
     float corr[2];
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
@@ -156,7 +181,6 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(SinkAttentionAr
       m_run[rr] = m_new;
     }
     float ps[2] = {0.f, 0.f};
-    unsigned pa[SA_KT / 16][4];                               // the weights as the value product's first operand, per 16 keys
 #pragma unroll
     for (int n = 0; n < SA_NT; ++n) {
       float pv[4];
@@ -181,6 +205,7 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(SinkAttentionAr
       acc[j][2] *= corr[1];
       acc[j][3] *= corr[1];
     }
+    }
     const unsigned v_addr = ds_smem(vtile + ((blk & 1) * 8 + (lane & 7)) * ldv + (blk >> 1) * 8);
 #pragma unroll
     for (int k2 = 0; k2 < SA_KT / 16; ++k2) {
@@ -201,7 +226,7 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(SinkAttentionAr
   for (int rr = 0; rr < 2; ++rr) {
     const int row = row0 + 8 * rr;
     if (row >= n_new) continue;
-    const float inv = l_run[rr] > 0.f ? 1.f / l_run[rr] : 0.f;
+    const float inv = SIGMOID ? 1.f : (l_run[rr] > 0.f ? 1.f / l_run[rr] : 0.f);
     const long long tok = first + row;
     __nv_bfloat16* dst = p.out + tok * p.out_row + (long long)head * p.out_head;
     const __nv_bfloat16* gt = p.gate ? p.gate + tok * p.gate_row + (long long)head * p.gate_head : nullptr;
@@ -235,7 +260,8 @@ extern "C" int bt_sink_attention(const void* q, long long q_row, int q_head, con
                                  const void* v, long long v_row, int v_head, const void* gate, long long gate_row,
                                  int gate_head, void* out, long long out_row, int out_head, const int* seq_start,
                                  const float* sink, int n_seqs, int max_new, int n_heads, int dq, int dv, float scale,
-                                 int window, cudaStream_t stream) {
+                                 int window, int keep_first, int kv_group, int sigmoid, const float* bias,
+                                 cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(bt_sink_attention_supports(dq, dv, q_row, q_head, k_row, k_head, v_row, v_head, gate_row, gate_head, out_row,
                                       out_head),
@@ -243,7 +269,9 @@ extern "C" int bt_sink_attention(const void* q, long long q_row, int q_head, con
   auto at = [](const void* ptr, int bytes) { return ((unsigned long long)ptr % bytes) == 0; };
   BT_CHECK(at(q, 16) && at(k, 16) && at(v, 16) && at(out, 4) && (gate == nullptr || at(gate, 4)),
            "sink_attention: operands must lie on 16-byte boundaries");
-  BT_CHECK(n_heads > 0 && n_heads <= 65535 && n_seqs <= 65535, "sink_attention: bad sizes heads=%d seqs=%d", n_heads, n_seqs);
+  BT_CHECK(n_heads > 0 && n_heads <= 65535 && n_seqs <= 65535 && kv_group > 0 && n_heads % kv_group == 0 && window >= 0 &&
+               keep_first >= 0,
+           "sink_attention: bad sizes heads=%d seqs=%d heads a key head=%d", n_heads, n_seqs, kv_group);
   if (n_seqs == 0 || max_new == 0) return 0;
   SinkAttentionArgs p;
   p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
@@ -251,12 +279,17 @@ extern "C" int bt_sink_attention(const void* q, long long q_row, int q_head, con
   p.q_row = q_row; p.k_row = k_row; p.v_row = v_row; p.gate_row = gate_row; p.out_row = out_row;
   p.q_head = q_head; p.k_head = k_head; p.v_head = v_head; p.gate_head = gate_head; p.out_head = out_head;
   p.seq_start = seq_start; p.sink = sink; p.dq = dq; p.dv = dv; p.scale = scale; p.window = window;
+  p.keep_first = keep_first; p.kv_group = kv_group; p.bias = bias;
   const int dqp = (dq + 15) & ~15, dvp = (dv + 15) & ~15;
   const size_t smem = (size_t)(SA_BM + 2 * SA_KT) * (dqp + SA_PAD) * 2 + (size_t)2 * SA_KT * (dvp + SA_PAD) * 2;
   const dim3 grid((max_new + SA_BM - 1) / SA_BM, n_heads, n_seqs), block(128);
 #define BT_SA(VCT)                                                                                                \
   do {                                                                                                            \
-    auto kernel = sink_attention_mma_kernel<VCT>;                                                                 \
+    if (sigmoid) BT_SA_KIND(VCT, true); else BT_SA_KIND(VCT, false);                                              \
+  } while (0)
+#define BT_SA_KIND(VCT, SIGMOID)                                                                                  \
+  do {                                                                                                            \
+    auto kernel = sink_attention_mma_kernel<VCT, SIGMOID>;                                                        \
     static size_t reserved = 0;                                                                                   \
     if (smem > 48 * 1024 && smem > reserved) {                                                                    \
       BT_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess, \
@@ -269,5 +302,6 @@ extern "C" int bt_sink_attention(const void* q, long long q_row, int q_head, con
   else if (dvp <= 64) BT_SA(64);
   else BT_SA(128);
 #undef BT_SA
+#undef BT_SA_KIND
   return 0;
 }

@@ -1088,26 +1088,36 @@ def sink_attention(q, k, v, out, seq_start, *, n_seqs, max_new, scale, sink=None
                                        c_longlong(vr), c_int(vh), _ptr(gate), c_longlong(gr), c_int(gh), _ptr(out),
                                        c_longlong(orow), c_int(oh), _ptr(seq_start), _ptr(sink), c_int(n_seqs),
                                        c_int(max_new), c_int(heads), c_int(dq), c_int(dv), c_float(scale), c_int(window),
-                                       _stream()))
+                                       c_int(0), c_int(1), c_int(0), c_void_p(0), _stream()))
 
 
 def latent_decode_prep(proj, q_off, latent_off, uk_heads, norm_weight, eps, positions, token_seq, inv_freq, rot_dims, table,
-                       table_len, pool, q_latent, *, n_tokens, n_heads, dim, rank, rot, owns):
+                       table_len, pool, q_latent, *, n_tokens, n_heads, dim, rank, rot, owns, latent_rows=None):
     """For steps of few tokens, in one launch: q_latent[t, h] = [W_uk,h^T q_plain | q_rot turned by the position], and
     (if `owns`) the token's own latent row normed, turned and filed in its page.  proj: [tokens, width] rows with the
-    queries at `q_off` (per head dim + rot channels) and the latent row at `latent_off`; uk_heads: [heads, dim, rank]."""
+    queries at `q_off` (per head dim + rot channels) and the latent row at `latent_off`, or, with `latent_rows` (a view
+    [tokens, rank + rot] with contiguous channels), the latent rows there; uk_heads: [heads, dim, rank]."""
     _need(proj, "proj", (torch.float32, torch.bfloat16))
+    if latent_rows is not None:
+        if (latent_rows.dim() != 2 or latent_rows.shape[1] != rank + rot or latent_rows.stride(1) != 1
+                or latent_rows.dtype is not proj.dtype or not latent_rows.is_cuda or latent_rows.shape[0] < n_tokens):
+            raise ShapeError(f"latent_decode_prep: latent_rows must be a device view [>= {n_tokens}, {rank + rot}] of the "
+                             f"queries' type with contiguous channels")
+        latent_off = 0
     _need(uk_heads, "uk_heads", proj.dtype, (n_heads, dim, rank))
     _need(pool, "pool", proj.dtype, (None, PAGE_SIZE, rank + rot))
     _need(q_latent, "q_latent", proj.dtype, (None, n_heads * (rank + rot)))
     _need(inv_freq, "inv_freq", torch.float32)
     if owns:
         _need(norm_weight, "norm_weight", torch.float32, (rank,))
-    if q_off + n_heads * (dim + rot) > proj.shape[1] or (owns and latent_off + rank + rot > proj.shape[1]):
+    if q_off + n_heads * (dim + rot) > proj.shape[1] or (owns and latent_rows is None
+                                                         and latent_off + rank + rot > proj.shape[1]):
         raise ShapeError("latent_decode_prep: the channel offsets leave the rows of proj")
     if proj.shape[0] < n_tokens or q_latent.shape[0] < n_tokens or inv_freq.numel() < rot_dims // 2:
         raise ShapeError("latent_decode_prep: too few rows or frequencies")
     _check(library().bt_latent_decode_prep(_ptr(proj), c_longlong(proj.shape[1]), c_int(q_off), c_int(latent_off),
+                                           _ptr(latent_rows),
+                                           c_longlong(latent_rows.stride(0) if latent_rows is not None else 0),
                                            _ptr(uk_heads), _ptr(norm_weight if owns else None), c_float(eps),
                                            _ptr(positions), _ptr(token_seq), _ptr(inv_freq), c_int(rot_dims), _ptr(table),
                                            c_int(table.shape[1]), c_int(table_len), c_int(PAGE_SIZE), _ptr(pool),
@@ -1399,8 +1409,8 @@ def sigmoid_attention_prep(proj, q_weight, k_weight, eps, positions, token_seq, 
     their first `rot_dims` channels turned by the position (channel i with channel i + rot_dims / 2, angle position *
     inv_freq[i]); value heads divided by their root mean square and, with `v_other` (32-bit [tokens, kv_heads * vdim]) and
     `mix` (a 32-bit number on the device), replaced by (1 - mix) v + mix v_other; `v_publish` receives the values as
-    they end up.  Queries are rewritten in place; keys and values go to the token's rows of `pool`
-    [pages, kv_heads, PAGE_SIZE, dim + vdim]."""
+    they end up.  Queries, keys and values are rewritten in place, and keys and values also go to the token's rows of
+    `pool` [pages, kv_heads, PAGE_SIZE, dim + vdim]."""
     width = (n_heads + n_kv_heads) * dim + n_kv_heads * vdim
     _need(proj, "proj", (torch.float32, torch.bfloat16), (None, width))
     _need(pool, "pool", proj.dtype, (None, n_kv_heads, PAGE_SIZE, dim + vdim))
@@ -1425,6 +1435,50 @@ def sigmoid_attention_prep(proj, q_weight, k_weight, eps, positions, token_seq, 
         _ptr(token_seq), _ptr(inv_freq), c_int(rot_dims), _ptr(mix), _ptr(v_other), _ptr(v_publish), _ptr(table),
         c_int(table.shape[1]), c_int(table_len), c_int(PAGE_SIZE), _ptr(pool), c_int(n_tokens), c_int(n_heads),
         c_int(n_kv_heads), c_int(dim), c_int(vdim), c_int(_code(proj.dtype)), _stream()))
+
+
+def _grouped_views(q, k, v, out):
+    """Strides of q [tokens, heads, dq], k [tokens, kv_heads, dq], v [tokens, kv_heads, dv], out [tokens, heads, dv]."""
+    heads, groups, dq, dv = q.shape[1], k.shape[1], q.shape[2], v.shape[2]
+    return (_head_view(q, "q", heads, dq), _head_view(k, "k", groups, dq), _head_view(v, "v", groups, dv),
+            _head_view(out, "out", heads, dv))
+
+
+def sigmoid_attention_prompt_supports(q, k, v, out) -> bool:
+    """Whether sigmoid_attention_prompt takes these views: bfloat16, whole 16-byte pieces per head and token, at most 128
+    value channels, operands on 16-byte boundaries, the query heads a multiple of the key heads."""
+    if any(t.dtype is not torch.bfloat16 for t in (q, k, v, out)) or q.shape[1] % k.shape[1] or v.shape[1] != k.shape[1]:
+        return False
+    (qr, qh), (kr, kh), (vr, vh), (orow, oh) = _grouped_views(q, k, v, out)
+    if any(t.data_ptr() % 16 for t in (q, k, v)) or out.data_ptr() % 4:
+        return False
+    return bool(library().bt_sink_attention_supports(c_int(q.shape[2]), c_int(v.shape[2]), c_longlong(qr), c_int(qh),
+                                                     c_longlong(kr), c_int(kh), c_longlong(vr), c_int(vh), c_longlong(0),
+                                                     c_int(0), c_longlong(orow), c_int(oh)))
+
+
+def sigmoid_attention_prompt(q, k, v, out, seq_start, *, n_seqs, max_new, scale, bias=None, window=0, keep_first=0):
+    """sigmoid_attention for sequences that start at position 0, on tensor cores (bfloat16), with keys and values read
+    from the step's own rows: q [tokens, heads, dq], k [tokens, kv_heads, dq], v [tokens, kv_heads, dv], out [tokens,
+    heads, dv] (views with contiguous channels).  Scores and sigmoids in 32-bit; a weight enters the value product
+    rounded to bfloat16, the sums are 32-bit."""
+    if not sigmoid_attention_prompt_supports(q, k, v, out):
+        raise ShapeError("sigmoid_attention_prompt: views the kernel does not take")
+    heads, groups = q.shape[1], k.shape[1]
+    (qr, qh), (kr, kh), (vr, vh), (orow, oh) = _grouped_views(q, k, v, out)
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (heads,))
+    if _PROFILE is not None:
+        ctx = float(_PROFILE.context_hint or 0)
+        seen = min(ctx / 2, float(window + keep_first)) if window else ctx / 2
+        _work(2.0 * q.shape[0] * heads * seen * (q.shape[2] + v.shape[2]),
+              2.0 * q.shape[0] * (heads * (q.shape[2] + v.shape[2]) + groups * (q.shape[2] + v.shape[2])))
+    _check(library().bt_sink_attention(_ptr(q), c_longlong(qr), c_int(qh), _ptr(k), c_longlong(kr), c_int(kh), _ptr(v),
+                                       c_longlong(vr), c_int(vh), c_void_p(0), c_longlong(0), c_int(0), _ptr(out),
+                                       c_longlong(orow), c_int(oh), _ptr(seq_start), c_void_p(0), c_int(n_seqs),
+                                       c_int(max_new), c_int(heads), c_int(q.shape[2]), c_int(v.shape[2]), c_float(scale),
+                                       c_int(window), c_int(keep_first), c_int(heads // groups), c_int(1), _ptr(bias),
+                                       _stream()))
 
 
 def sigmoid_attention(q, out, pool, table, table_len, seq_start, past_len, *, n_seqs, max_new, n_heads, n_kv_heads, dim,

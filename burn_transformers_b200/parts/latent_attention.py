@@ -145,14 +145,16 @@ class LatentAttention(Mixer):
         pool = k_pool.view(-1, PAGE_SIZE, dk)
         table = ctx.tables[g]
         freq = self.positions.inv_freq(proj.device)
-        if n <= self.fused_up_to and self.q_rank is None and self.has_gate:
+        if n <= self.fused_up_to:
             # few tokens: query into the latent space + rotation + filing in one launch, the attention, then
             # join of the splits + W_uv + gate in one launch
             q_latent = ctx.ws.take((n, heads * dk), dtype)
-            kernels.latent_decode_prep(proj, 0, self.q_width + self.gate_width, self.uk_heads,
+            kernels.latent_decode_prep(queries, 0, latent_off, self.uk_heads,
                                        self.t_latent_norm_weight if self.owns_latent else None, self.eps, ctx.positions,
                                        ctx.token_seq, freq, self.positions.dims, table, group.table_len, pool, q_latent,
-                                       n_tokens=n, n_heads=heads, dim=self.dim, rank=rank, rot=rot, owns=self.owns_latent)
+                                       n_tokens=n, n_heads=heads, dim=self.dim, rank=rank, rot=rot, owns=self.owns_latent,
+                                       latent_rows=proj[:, latent_off:] if self.owns_latent and queries is not proj
+                                       else None)
             mixed_latent = ctx.ws.take((n, heads * rank), dtype)
             splits = self._splits(ctx, kernels.latent_attention_rows(rank, rot, dtype))
             scratch = None
@@ -162,10 +164,10 @@ class LatentAttention(Mixer):
                                      n_tokens=n, n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=heads, rank=rank, rot=rot,
                                      scale=self.scale, sink=self.t_sink if self.has_sink else None, n_splits=splits,
                                      scratch=scratch, merge=False, window=window)
-            mixed = ctx.ws.take((n, self.gate_width), dtype)
+            mixed = ctx.ws.take((n, self.mixed_width), dtype)
             kernels.latent_decode_finish(self.uv_heads, mixed, n_tokens=n, n_splits=splits, scratch=scratch,
                                          mixed_latent=mixed_latent,
-                                         gate=proj[:, self.q_width:self.q_width + self.gate_width])
+                                         gate=proj[:, gate_off:latent_off] if self.has_gate else None)
             linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)
             ctx.ws.release(mark)
             return

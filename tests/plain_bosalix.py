@@ -93,11 +93,16 @@ def visible(i, j, size, keep_first):
     return i - j < size or j < keep_first
 
 
-def latent_attention(h, w, m, eps, first_position=0):
+def visibility(n, size, keep_first):
+    """[n, n] of booleans: row i, column j."""
+    return torch.tensor([[visible(i, j, size, keep_first) for j in range(n)] for i in range(n)])
+
+
+def latent_attention(h, w, m, eps):
     """h [tokens, width] of one sequence from its first token; w: the mixer's tensors by short name."""
     n = h.shape[0]
     heads, dim, rot, vdim, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-    positions = torch.arange(first_position, first_position + n)
+    positions = torch.arange(n)
     cq = norm_plain(h @ w["dq"].T, w["dq.norm"], eps)
     q = (cq @ w["uq"].T).view(n, heads, dim + rot)
     down = h @ w["dkv"].T
@@ -108,14 +113,12 @@ def latent_attention(h, w, m, eps, first_position=0):
     k_plain = (c @ w["uk"].T).view(n, heads, dim)
     v = (c @ w["uv"].T).view(n, heads, vdim)
     size = m.get("mask", {}).get("size") if m.get("mask") else None
+    seen = visibility(n, size, 0)
     out = torch.zeros(n, heads, vdim, dtype=F64)
     for head in range(heads):
-        for i in range(n):
-            seen = [j for j in range(n) if visible(i, j, size, 0)]
-            scores = torch.stack([(q[i, head, :dim] @ k_plain[j, head] + q_rot[i, head] @ shared[j]) * m["scale"]
-                                  for j in seen])
-            p = torch.softmax(scores, 0)
-            out[i, head] = sum(p[a] * v[j, head] for a, j in enumerate(seen))
+        scores = (q[:, head, :dim] @ k_plain[:, head].T + q_rot[:, head] @ shared.T) * m["scale"]      # [query, key]
+        p = torch.softmax(scores.masked_fill(~seen, -math.inf), -1)
+        out[:, head] = p @ v[:, head]
     return out.reshape(n, heads * vdim) @ w["o"].T
 
 
@@ -141,14 +144,12 @@ def sigmoid_attention(h, w, m, eps, v_first=None):
         v = (1.0 - lam) * v + lam * v_first
     mask = m.get("mask") or {}
     size, keep = mask.get("size"), mask.get("keep_first", 0)
+    seen = visibility(n, size, keep)
     out = torch.zeros(n, heads, vdim, dtype=F64)
     for head in range(heads):
         g = head // (heads // groups)
-        for i in range(n):
-            for j in range(i + 1):
-                if visible(i, j, size, keep):
-                    weight = torch.sigmoid((q[i, head] @ k[j, g]) * m["scale"] + w["pb"][head])
-                    out[i, head] += weight * v[j, g]
+        weights = torch.sigmoid((q[:, head] @ k[:, g].T) * m["scale"] + w["pb"][head])      # [query, key], not normalised
+        out[:, head] = (weights * seen) @ v[:, g]
     return out.reshape(n, heads * vdim) @ w["o"].T + w["o.b"], v
 
 
@@ -170,20 +171,24 @@ def routed_experts(h, w, mlp):
     return out
 
 
+def as_f64(value):
+    return value.to(F64) if isinstance(value, torch.Tensor) else torch.as_tensor(value, dtype=F64)
+
+
 def layer_tensors(tensors, i, part):
     prefix = f"l{i}.{part}."
-    return {k[len(prefix):]: v.to(F64) for k, v in tensors.items() if k.startswith(prefix)}
+    return {k[len(prefix):]: as_f64(v) for k, v in tensors.items() if k.startswith(prefix)}
 
 
 def forward(config, tensors, tokens, keep_layers=False):
     """Logits [tokens, vocab] of one sequence (and the stream after every layer)."""
     eps, mult = config["norm"]["eps"], config["residual_mult"]
-    x = tensors["embed"].to(F64)[torch.tensor(tokens)] * config["embedding"]["scale"]
+    x = as_f64(tensors["embed"])[torch.tensor(tokens)] * config["embedding"]["scale"]
     v_first = None
     stream = []
     for i, layer in enumerate(config["layers"]):
         m = layer["mixer"]
-        h, _ = token_shift(x, tensors[f"l{i}.shift"].to(F64))
+        h, _ = token_shift(x, as_f64(tensors[f"l{i}.shift"]))
         w = layer_tensors(tensors, i, "mix")
         if layer["type"] == "latent_attention":
             mixed = latent_attention(h, w, m, eps)
@@ -192,10 +197,10 @@ def forward(config, tensors, tokens, keep_layers=False):
             mixed, v = sigmoid_attention(h, w, m, eps, v_first if mixing else None)
             if mixing and v_first is None:
                 v_first = v
-        x = x + mult * norm_around_zero(mixed, tensors[f"l{i}.norm1"].to(F64), eps)
+        x = x + mult * norm_around_zero(mixed, as_f64(tensors[f"l{i}.norm1"]), eps)
         if layer.get("mlp") is not None:
             y = routed_experts(x, layer_tensors(tensors, i, "mlp"), layer["mlp"])
-            x = x + mult * norm_around_zero(y, tensors[f"l{i}.norm2"].to(F64), eps)
+            x = x + mult * norm_around_zero(y, as_f64(tensors[f"l{i}.norm2"]), eps)
         stream.append(x.clone())
-    logits = norm_around_zero(x, tensors["final.norm"].to(F64), eps) @ tensors["head"].to(F64).T
-    return (logits, torch.stack(stream)) if keep_layers else logits
+    logits = norm_around_zero(x, as_f64(tensors["final.norm"]), eps) @ as_f64(tensors["head"]).T
+    return (logits, torch.stack(stream)) if keep_layers else logits.numpy()
