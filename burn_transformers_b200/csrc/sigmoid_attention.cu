@@ -201,29 +201,44 @@ sigmoid_attention_kernel(const T* __restrict__ q, long long q_row_stride, const 
   }
 }
 
-// Steps of one token a sequence.  grid: (key heads x head tiles, sequences); a block holds up to SD_ROWS query heads of
-// one key head, and its W warps share the KEYS: warp w takes the visible key tiles w, w + W, ... (first those that hold
-// kept first positions and lie before the window, then the window's), each into shared memory of its own, so no block
-// barrier stands between tiles.  For the scores a lane is a key and holds all rows' scores; for the value sum a lane
-// is a set of value channels.  The warps' partial sums meet in shared memory and are added in warp order: which warp
-// takes which tile depends on the token's position and the window only, so the sum's order does not depend on what
-// else the step holds.
-constexpr int SD_ROWS = 8;
+// Steps of one token a sequence.  grid: (key heads x head tiles, sequences); a block holds up to SD_ROWS (2, 4 or 8) query
+// heads of one key head, and its W warps (up to 16) share the KEYS: warp w takes the visible key tiles w, w + W, ...
+// (first those that hold kept first positions and lie before the window, then the window's), each into shared memory
+// of its own, so no block barrier stands between tiles.  A tile lies in shared memory as it lies in the page, in the
+// cache's element type (16-byte pieces in, 4-byte pieces down; key rows two elements apart from a whole number of
+// banks), the queries as 32-bit numbers with a channel's rows side by side (one 16-byte read a channel and four rows).
+// For the scores a lane is a key and holds all rows' scores; for the value sum a lane is a set of value channels.  The
+// warps' partial sums meet in shared memory and are added in warp order: which warp takes which tile depends on the
+// token's position and the window only, so the sum's order does not depend on what else the step holds.
+template <typename T> struct SdPiece;
+template <> struct SdPiece<float> {            // a 4-byte piece: one number
+  static constexpr int N = 1;
+  __device__ static void read(const float* p, float (&o)[2]) { o[0] = *p; o[1] = 0.f; }
+};
+template <> struct SdPiece<__nv_bfloat16> {    // a 4-byte piece: two numbers
+  static constexpr int N = 2;
+  __device__ static void read(const __nv_bfloat16* p, float (&o)[2]) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    o[0] = f.x; o[1] = f.y;
+  }
+};
 
-template <typename T, int DVL>
-__global__ void __launch_bounds__(256)
+template <typename T, int SD_ROWS, int DVL>
+__global__ void __launch_bounds__(512)
 sigmoid_attention_decode_kernel(const T* __restrict__ q, long long q_row_stride, const T* __restrict__ pool,
                                 const int* __restrict__ table, int table_stride, int table_len, int page_size,
                                 const int* __restrict__ seq_start, const int* __restrict__ past_len,
                                 const float* __restrict__ bias, T* __restrict__ out, long long out_row_stride,
-                                int n_heads, int n_kv_heads, int head_tiles, int dim, int vdim, float scale, int window,
-                                int keep_first) {
-  extern __shared__ float smem[];
+                                int n_heads, int n_kv_heads, int head_tiles, int dim, int vdim, int ks, float scale,
+                                int window, int keep_first) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int PN = SdPiece<T>::N;              // numbers in a 4-byte piece
   const int n_warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int ks = dim + 1, dkv = dim + vdim;
-  float* q_s = smem;                                              // [SD_ROWS][dim]
-  float* k_s = q_s + SD_ROWS * dim + (size_t)warp * SG_TK * (ks + vdim);   // this warp's [SG_TK][ks]
-  float* v_s = k_s + SG_TK * ks;                                  // this warp's [SG_TK][vdim]
+  const int dkv = dim + vdim;
+  float* q_s = smem;                                              // [dim][SD_ROWS]
+  const int tile_words = (SG_TK * (ks + vdim) * (int)sizeof(T) + 3) / 4;
+  T* k_s = reinterpret_cast<T*>(q_s + SD_ROWS * dim + (size_t)warp * tile_words);   // this warp's [SG_TK][ks]
+  T* v_s = k_s + SG_TK * ks;                                      // this warp's [SG_TK][vdim]
   pdl_trigger();
   pdl_wait();
   const int seq = blockIdx.y, g = blockIdx.x / head_tiles, head_tile = blockIdx.x - g * head_tiles;
@@ -234,7 +249,7 @@ sigmoid_attention_decode_kernel(const T* __restrict__ q, long long q_row_stride,
   const int pos = past_len[seq];
   for (int i = threadIdx.x; i < SD_ROWS * dim; i += blockDim.x) {
     const int r = i / dim, d = i - r * dim;
-    q_s[i] = r < rows ? to_float(q[token * q_row_stride + (long long)(h0 + r) * dim + d]) : 0.f;
+    q_s[d * SD_ROWS + r] = r < rows ? to_float(q[token * q_row_stride + (long long)(h0 + r) * dim + d]) : 0.f;
   }
   __syncthreads();
   float row_bias[SD_ROWS], acc[SD_ROWS][DVL];
@@ -248,47 +263,82 @@ sigmoid_attention_decode_kernel(const T* __restrict__ q, long long q_row_stride,
   const int window_tile = window > 0 ? max(0, pos - window + 1) / SG_TK : 0;
   const int kept_only = window > 0 ? min((min(keep_first, pos + 1) + SG_TK - 1) / SG_TK, window_tile) : 0;
   const int n_visible = kept_only + n_tiles - window_tile;
+  // whole 16-byte pieces that lie in the keys or in the values, never across (else element by element)
+  constexpr int V = 16 / (int)sizeof(T);
+  const bool pieces_ok = dim % V == 0 && vdim % V == 0 && ks % PN == 0 && (reinterpret_cast<unsigned long long>(pool) & 15) == 0;
   for (int idx = warp; idx < n_visible; idx += n_warps) {
     const int tile = idx < kept_only ? idx : window_tile + (idx - kept_only);
     const int j0 = tile * SG_TK;
     __syncwarp();          // the lanes are done with the tile before
-    for (int kk = 0; kk < SG_TK; ++kk) {
-      const int j = j0 + kk;
-      if (j <= pos) {
-        const int lp = j / page_size;
-        const long long page = table[(long long)seq * table_stride + (lp % table_len)];
-        const T* src = pool + (((page * n_kv_heads + g) * page_size) + (j - lp * page_size)) * dkv;
-        for (int d = lane; d < dkv; d += 32) {
-          const float v = to_float(src[d]);
-          if (d < dim) k_s[kk * ks + d] = v; else v_s[kk * vdim + d - dim] = v;
-        }
-      } else {
-        for (int d = lane; d < dkv; d += 32)
-          if (d < dim) k_s[kk * ks + d] = 0.f; else v_s[kk * vdim + d - dim] = 0.f;
+    // a tile of 32 positions never straddles a page (pages hold a multiple of 32 positions), and the rows of one key
+    // head lie one after another in a page: the tile is one run of 32 * (dim + vdim) elements.  Positions past the
+    // token's own hold whatever an earlier sequence left there (finite numbers): their weights are zero.
+    const int lp = j0 / page_size;
+    const long long page = table[(long long)seq * table_stride + (lp % table_len)];
+    const T* src = pool + (((page * n_kv_heads + g) * page_size) + (j0 - lp * page_size)) * dkv;
+    if (pieces_ok) {
+      const int per_row = dkv / V, n_pieces = SG_TK * per_row;
+#pragma unroll 8
+      for (int i = lane; i < n_pieces; i += 32) {
+        const int kk = i / per_row, d0 = (i - kk * per_row) * V;
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + (long long)i * V);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(d0 < dim ? k_s + kk * ks + d0 : v_s + kk * vdim + (d0 - dim));
+        dst[0] = raw.x; dst[1] = raw.y; dst[2] = raw.z; dst[3] = raw.w;
+      }
+    } else {
+      for (int i = lane; i < SG_TK * dkv; i += 32) {
+        const int kk = i / dkv, d = i - kk * dkv;
+        if (d < dim) k_s[kk * ks + d] = src[i]; else v_s[kk * vdim + d - dim] = src[i];
       }
     }
     __syncwarp();
     float s[SD_ROWS];
 #pragma unroll
     for (int r = 0; r < SD_ROWS; ++r) s[r] = 0.f;
-    const float* krow = k_s + lane * ks;
-    for (int d = 0; d < dim; ++d) {
-      const float kv = krow[d];
+    const T* krow = k_s + lane * ks;
+    int d = 0;
+    if (ks % PN == 0) {
+#pragma unroll 4
+      for (; d + PN <= dim; d += PN) {
+        float kv[2];
+        SdPiece<T>::read(krow + d, kv);
 #pragma unroll
-      for (int r = 0; r < SD_ROWS; ++r) s[r] = fmaf(q_s[r * dim + d], kv, s[r]);
+        for (int u = 0; u < PN; ++u) {
+          const float* qd = q_s + (d + u) * SD_ROWS;
+          if (SD_ROWS % 4 == 0) {
+#pragma unroll
+            for (int r4 = 0; r4 < SD_ROWS / 4; ++r4) {
+              const float4 qv = *reinterpret_cast<const float4*>(qd + 4 * r4);
+              s[4 * r4 + 0] = fmaf(qv.x, kv[u], s[4 * r4 + 0]);
+              s[4 * r4 + 1] = fmaf(qv.y, kv[u], s[4 * r4 + 1]);
+              s[4 * r4 + 2] = fmaf(qv.z, kv[u], s[4 * r4 + 2]);
+              s[4 * r4 + 3] = fmaf(qv.w, kv[u], s[4 * r4 + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int r = 0; r < SD_ROWS; ++r) s[r] = fmaf(qd[r], kv[u], s[r]);
+          }
+        }
+      }
+    }
+    for (; d < dim; ++d) {
+      const float kv = to_float(krow[d]);
+#pragma unroll
+      for (int r = 0; r < SD_ROWS; ++r) s[r] = fmaf(q_s[d * SD_ROWS + r], kv, s[r]);
     }
     const int j = j0 + lane, gap = pos - j;
     const bool seen = gap >= 0 && (window <= 0 || gap < window || j < keep_first);
 #pragma unroll
     for (int r = 0; r < SD_ROWS; ++r) s[r] = seen ? 1.f / (1.f + expf(-(s[r] * scale + row_bias[r]))) : 0.f;
-    for (int kk = 0; kk < SG_TK; ++kk) {
+    const int kk_end = min(SG_TK, pos - j0 + 1);        // (rows past the token's own are never read)
+    for (int kk = 0; kk < kk_end; ++kk) {
       float pk[SD_ROWS];
 #pragma unroll
       for (int r = 0; r < SD_ROWS; ++r) pk[r] = __shfl_sync(0xffffffffu, s[r], kk);
 #pragma unroll
       for (int jj = 0; jj < DVL; ++jj) {
         const int c = lane + 32 * jj;
-        const float v = c < vdim ? v_s[kk * vdim + c] : 0.f;
+        const float v = c < vdim ? to_float(v_s[kk * vdim + c]) : 0.f;
 #pragma unroll
         for (int r = 0; r < SD_ROWS; ++r) acc[r][jj] = fmaf(pk[r], v, acc[r][jj]);
       }
@@ -320,21 +370,35 @@ static int launch_sigmoid_attention_decode(const T* q, long long q_row_stride, c
                                            int n_seqs, int n_heads, int n_kv_heads, int dim, int vdim, float scale,
                                            int window, int keep_first, cudaStream_t stream) {
   const int group_heads = n_heads / n_kv_heads;
-  const int head_tiles = (group_heads + SD_ROWS - 1) / SD_ROWS;
+  const int sd_rows = group_heads <= 2 ? 2 : group_heads <= 4 ? 4 : 8;      // rows a lane keeps scores of
+  const int head_tiles = (group_heads + sd_rows - 1) / sd_rows;
   const int dvl = (vdim + 31) / 32;
-  // as many warps as their key and value tiles fit into shared memory (the sums reuse the tiles' place: smaller)
-  int warps = 8;
-  auto bytes = [&](int w) { return ((size_t)SD_ROWS * dim + (size_t)w * SG_TK * (dim + 1 + vdim)) * sizeof(float); };
+  BT_CHECK(page_size % SG_TK == 0, "sigmoid_attention: pages of %d positions are no whole tiles of %d", page_size, SG_TK);
+  // a key row's length in shared memory: a whole number of 4-byte pieces, and an odd number of them, so that the lanes'
+  // rows start in different banks
+  const int per_word = 4 / (int)sizeof(T);
+  int ks = (dim + per_word - 1) / per_word * per_word;
+  if ((ks / per_word) % 2 == 0) ks += per_word;
+  // as many warps as their tiles fit into shared memory (the warps' sums reuse the tiles' place and are smaller)
+  const size_t tile_words = ((size_t)SG_TK * (ks + vdim) * sizeof(T) + 3) / 4;
+  auto bytes = [&](int w) {
+    const size_t tiles = (size_t)w * tile_words, sums = (size_t)w * sd_rows * vdim;
+    return ((size_t)sd_rows * dim + (tiles > sums ? tiles : sums)) * sizeof(float);
+  };
+  int warps = 16;
   while (warps > 1 && bytes(warps) > 160 * 1024) warps >>= 1;
   const size_t smem = bytes(warps);
   BT_CHECK(smem <= 200 * 1024, "sigmoid_attention: heads of %d + %d channels need %zu bytes of shared memory", dim, vdim,
            smem);
-  BT_CHECK(n_kv_heads * head_tiles <= 65535 * 32 && n_seqs <= 65535, "sigmoid_attention: bad sizes kv_heads=%d seqs=%d",
-           n_kv_heads, n_seqs);
+  BT_CHECK(n_seqs <= 65535, "sigmoid_attention: %d sequences are more than a launch takes", n_seqs);
   const dim3 grid(n_kv_heads * head_tiles, n_seqs), block(warps * 32);
 #define BT_SD(DVL)                                                                                                     \
   do {                                                                                                                 \
-    auto kernel = sigmoid_attention_decode_kernel<T, DVL>;                                                             \
+    if (sd_rows == 2) BT_SD_ROWS(2, DVL); else if (sd_rows == 4) BT_SD_ROWS(4, DVL); else BT_SD_ROWS(8, DVL);          \
+  } while (0)
+#define BT_SD_ROWS(ROWS, DVL)                                                                                          \
+  do {                                                                                                                 \
+    auto kernel = sigmoid_attention_decode_kernel<T, ROWS, DVL>;                                                       \
     if (smem > 48 * 1024) {                                                                                            \
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
       BT_CHECK(e == cudaSuccess, "sigmoid_attention: cannot reserve %zu bytes of shared memory", smem);                \
@@ -342,13 +406,14 @@ static int launch_sigmoid_attention_decode(const T* q, long long q_row_stride, c
     BT_PDL_OK("sigmoid_attention_decode",                                                                              \
               launch_pdl(kernel, grid, block, smem, stream, 1, q, q_row_stride, pool, table, table_stride, table_len,  \
                          page_size, seq_start, past_len, bias, out, out_row_stride, n_heads, n_kv_heads, head_tiles,   \
-                         dim, vdim, scale, window, keep_first));                                                       \
+                         dim, vdim, ks, scale, window, keep_first));                                                   \
   } while (0)
   if (dvl <= 1) BT_SD(1);
   else if (dvl <= 2) BT_SD(2);
   else if (dvl <= 4) BT_SD(4);
   else BT_SD(8);
 #undef BT_SD
+#undef BT_SD_ROWS
   return 0;
 }
 
