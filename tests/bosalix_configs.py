@@ -54,7 +54,7 @@ def model(vocab, width, eps, mult, embed_scale, layers):
 # query heads a key head; windows of 40, 70 and 100 with 5, 0 and 90 kept first positions, and one layer that sees
 # everything; rotations of a part of the head and of all of it, with and without stretched frequencies; latent layers
 # with and without a window; layers without a feed-forward; experts with and without ones that hand their input on.
-MIXED = model(310, 96, 1e-5, 0.5, 9.0, [
+MIXED = model(310, 96, 1e-5, 0.6, 9.0, [
     attention(6, 2, 24, 16, 0.2, 16, 10000.0, window=40, keep_first=5, scaling=(4.0, 1.0, 4.0, 64), v_mix=True,
               mlp=moe(6, 2, 2, 40)),
     latent(3, 16, 8, 24, 48, 40, 0.2, 5000.0, window=33, mlp=moe(4, 0, 1, 56)),
@@ -75,10 +75,10 @@ ODD = model(257, 72, 1e-6, 1.3, 1.0, [
     latent(5, 6, 2, 6, 12, 30, 0.4, 7.0, window=2),
 ])
 
-# C: larger heads (other branches of the kernels' size tables): 128 and 72 key channels a head, values of 130 channels, a
+# C: larger heads (other branches of the kernels' size tables): 128 and 72 key channels a head, values of 96 and 130 channels, a
 # latent of 160 channels, sixteen query heads a key head.
 LARGE = model(150, 80, 1e-5, 0.7, 4.0, [
-    attention(16, 1, 128, 64, 0.09, 64, 1e6, window=70, keep_first=16, v_mix=True, mlp=moe(8, 4, 2, 96)),
+    attention(16, 1, 128, 96, 0.09, 48, 1e6, window=70, keep_first=16, v_mix=True, mlp=moe(10, 3, 2, 88)),
     latent(6, 32, 16, 32, 160, 96, 0.14, 50000.0, window=50, mlp=moe(4, 4, 2, 64)),
     attention(4, 2, 72, 130, 0.12, 72, 10000.0, window=130, keep_first=1),
 ])

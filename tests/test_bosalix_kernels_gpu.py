@@ -108,7 +108,7 @@ def sigmoid_case(rng, heads, groups, dim, vdim, rot_dims, news, pasts, dtype, mi
 @pytest.mark.parametrize("heads, groups, dim, vdim, rot_dims, window, keep, mixing", [
     (6, 2, 24, 16, 16, 40, 5, True),          # a window and kept positions inside one page
     (5, 1, 12, 10, 6, 70, 66, False),         # sizes that are no 16-byte pieces; kept positions past a page's border
-    (16, 1, 128, 64, 64, 64, 0, True),        # a window of exactly one page, sixteen heads a key head
+    (16, 1, 128, 96, 48, 64, 0, True),        # a window of exactly one page, sixteen heads a key head
     (40, 1, 16, 8, 0, 3, 1, False),           # more heads a key head than a block's rows; no rotation
     (2, 2, 72, 130, 72, 0, 0, False),         # no window at all; wide values
     (3, 3, 8, 40, 8, 1, 200, True),           # a window of one token, more kept positions than any sequence is long
