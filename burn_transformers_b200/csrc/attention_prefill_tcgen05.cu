@@ -25,6 +25,11 @@
 // a sequence's end in a tile is finite (rows of the next sequence, zero fill past the tensor, old page contents).
 // All hand-overs go through mbarriers; every wait is bounded, and a wait that runs out sets the status word:
 // the block still frees its tensor memory and returns.
+//
+// SIGMOID is the same walk for attention without a softmax: the weight of a visible key is sigmoid(score * scale +
+// bias[head]) and nothing is normalised, so the two threads of a row exchange no maximum, nothing is rescaled and
+// nothing divided at the end.  With a window, positions below `keep_first` stay visible to every later query: the tiles
+// that hold them and lie before the window's first tile are walked first (the products never ask where a tile lies).
 #include "api.h"
 #include "common.cuh"
 #include "tma.cuh"
@@ -49,6 +54,8 @@ struct TaParams {
   int k_col, v_col;            // packed: first column of the keys / values in a row of the projections
   float scale_log2;            // scale * log2(e)
   int causal, window;
+  int keep_first;              // SIGMOID, with a window: positions below this stay visible
+  const float* bias;           // SIGMOID: a number per head added to the scaled score (may be null)
 };
 
 __device__ __forceinline__ unsigned ta_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -152,7 +159,7 @@ constexpr size_t ta_smem_bytes() {
   return (size_t)(HD / 64) * 2 * TA_BOX_BYTES * (1 + 2 * TA_STAGES) + 2 * 2 * 2 * TA_BOX_BYTES + 4 * 128 * 4 + 256;
 }
 
-template <int HD>
+template <int HD, bool SIGMOID>
 __global__ void __launch_bounds__(TA_THREADS, 1)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                                  const __grid_constant__ CUtensorMap v_map, TaParams p) {
@@ -203,7 +210,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
   if (p.causal) key_hi = min(key_hi, pos_last);
   if (p.window > 0) key_lo = max(0, pos_first - p.window + 1);
   const int kt_lo = key_lo / TA_BK, kt_hi = key_hi / TA_BK;
-  const int n_tiles = kt_hi - kt_lo + 1;
+  // tiles before the window's first that hold kept first positions (SIGMOID): walked first
+  const int kept_only = SIGMOID && p.window > 0 ? min((min(p.keep_first, key_hi + 1) + TA_BK - 1) / TA_BK, kt_lo) : 0;
+  const int n_tiles = kept_only + kt_hi - kt_lo + 1;
+  auto tile_at = [&](int it) { return it < kept_only ? it : kt_lo + (it - kept_only); };
 
   if (threadIdx.x == 0) {
     ta_bar_init(q_full, 1);
@@ -242,7 +252,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
           ta_tma(Qs + cb * 2 * TA_BOX_BYTES + h * TA_BOX_BYTES, &q_map, head * HD + cb * 64, t0 + q0 + h * 64, q_full);
       // where the 64 keys of half h of tile `it` lie: their row in the tensor and the first columns of K and V
       auto where = [&](int it, int h, int& row, int& col_k, int& col_v) {
-        const int kt = kt_lo + it;
+        const int kt = tile_at(it);
         if (p.table) {
           // a page is one box; a half tile beyond the sequence's end repeats its last page (masked, but finite)
           const int key = min(kt * TA_BK + h * 64, kv_len - 1);
@@ -393,13 +403,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
     // (after a wait has run out the remaining waits are skipped, but every warp still runs every tile: the two
     // warps of a row meet at a barrier in each)
     for (int it = 0; it < n_tiles; ++it) {
-      const int key0 = (kt_lo + it) * TA_BK;
+      const int key0 = tile_at(it) * TA_BK;
       const unsigned s_addr = tmem_s + lane_base + (unsigned)((it & 1) * TA_BK + half * 64);
       if (ok && !ta_bar_wait(&s_full[it & 1], (it >> 1) & 1)) ok = false;
       ta_fence_after();
       // every key of the tile visible to every query of the block?  Then nothing is masked (the common tile).
       const bool whole = key0 + TA_BK <= kv_len && (!p.causal || key0 + TA_BK - 1 <= pos_first) &&
-                         (p.window <= 0 || key0 > pos_last - p.window) && p.scale_log2 > 0.f;
+                         (p.window <= 0 || key0 > pos_last - p.window) && (SIGMOID || p.scale_log2 > 0.f);
       int lo = 0, hi = kv_len - 1;          // this row's visible keys, then relative to this thread's 64 keys
       if (p.causal) hi = min(hi, pos);
       if (p.window > 0) lo = max(0, pos - p.window + 1);
@@ -409,6 +419,28 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
       ta_ld32_issue(s_addr, a);
       ta_ld32_issue(s_addr + 32u, b);
       ta_ld_wait(a, b);
+      float sum = 0.f, alpha = 1.f, m_new = m;
+      float va[32], vb[32];
+      if constexpr (SIGMOID) {
+        // a weight is 1 / (1 + 2^-(score * scale + bias)) in base 2; kept first positions count beside the window's
+        const int kept = min(p.keep_first, pos + 1) - (key0 + half * 64);      // this thread's keys below it are seen
+        const float bias2 = p.bias != nullptr ? p.bias[head] * 1.4426950408889634f : 0.f;
+        if (whole) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            va[i] = __fdividef(1.f, 1.f + ta_exp2(-fmaf(__uint_as_float(a[i]), p.scale_log2, bias2)));
+            vb[i] = __fdividef(1.f, 1.f + ta_exp2(-fmaf(__uint_as_float(b[i]), p.scale_log2, bias2)));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const bool sa = (i >= lo && i <= hi) || (p.window > 0 && i < kept && i <= hi);
+            const bool sb = (i + 32 >= lo && i + 32 <= hi) || (p.window > 0 && i + 32 < kept && i + 32 <= hi);
+            va[i] = sa ? __fdividef(1.f, 1.f + ta_exp2(-fmaf(__uint_as_float(a[i]), p.scale_log2, bias2))) : 0.f;
+            vb[i] = sb ? __fdividef(1.f, 1.f + ta_exp2(-fmaf(__uint_as_float(b[i]), p.scale_log2, bias2))) : 0.f;
+          }
+        }
+      } else {
       // the row's maximum over this thread's keys, then over the row (the other thread's through shared memory)
       float tile_max = -INFINITY;
       if (whole) {
@@ -426,12 +458,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
       // the two warps of a quarter meet at a barrier of their own (64 threads); both run every tile, see below
       asm volatile("bar.sync %0, 64;\n" ::"r"(1 + (warp & 3)) : "memory");
       tile_max = fmaxf(tile_max, x_max[((it & 1) * 2 + (half ^ 1)) * 128 + r]);
-      const float m_new = fmaxf(m, tile_max);
+      m_new = fmaxf(m, tile_max);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = ta_exp2(m - m_use);         // 0 for a row that had seen nothing yet
+      alpha = ta_exp2(m - m_use);         // 0 for a row that had seen nothing yet
       // weights, their sum, and P in shared memory: this thread's 64 keys are one box's row of 128 bytes
-      float sum = 0.f;
-      float va[32], vb[32];
       if (whole) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -446,6 +476,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
           vb[i] = (i + 32 >= lo && i + 32 <= hi) ? ta_exp2(fmaf(__uint_as_float(b[i]), p.scale_log2, -m_use)) : 0.f;
           sum += va[i] + vb[i];
         }
+      }
       }
       // (this P tile is free: its last products, of tile it - 2, were waited for before that tile's O was taken)
       unsigned char* box = Ps + (it & 1) * 2 * 2 * TA_BOX_BYTES + half * 2 * TA_BOX_BYTES + r * 128;
@@ -477,21 +508,25 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         ta_fence_after();
         take_o(it - 1);
       }
+      if constexpr (!SIGMOID) {
 #pragma unroll
-      for (int i = 0; i < HH; ++i) o[i] *= alpha;
+        for (int i = 0; i < HH; ++i) o[i] *= alpha;
+      }
     }
     if (ok && !ta_bar_wait(&o_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) ok = false;
     ta_fence_after();
     take_o(n_tiles - 1);
     // the row's sum is the two threads' (both hold the same maximum)
     // (through the exchange buffer that the last tile did not use: nobody reads that one any more)
-    float* x_sum = x_max + (n_tiles & 1) * 2 * 128;
-    x_sum[half * 128 + r] = l;
-    asm volatile("bar.sync %0, 64;\n" ::"r"(1 + (warp & 3)) : "memory");
-    l += x_sum[(half ^ 1) * 128 + r];
+    if constexpr (!SIGMOID) {
+      float* x_sum = x_max + (n_tiles & 1) * 2 * 128;
+      x_sum[half * 128 + r] = l;
+      asm volatile("bar.sync %0, 64;\n" ::"r"(1 + (warp & 3)) : "memory");
+      l += x_sum[(half ^ 1) * 128 + r];
+    }
     if (!ok) *failed = 1;
     if (ok && r < nq) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const float inv = SIGMOID ? 1.f : (l > 0.f ? 1.f / l : 0.f);
       __nv_bfloat16* dst = p.out + (long long)(t0 + q0 + r) * ((long long)p.n_heads * HD) + head * HD + half * HH;
 #pragma unroll
       for (int c = 0; c < HH; c += 8) {
@@ -513,11 +548,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
   if (threadIdx.x == 0 && *failed && p.status) atomicExch(p.status, 6);
 }
 
-template <int HD>
+template <int HD, bool SIGMOID>
 static int launch_ta(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const TaParams& p, int n_seqs, int max_new,
                      cudaStream_t stream) {
   constexpr size_t smem = ta_smem_bytes<HD>();
-  auto kern = attention_prefill_tcgen05_kernel<HD>;
+  auto kern = attention_prefill_tcgen05_kernel<HD, SIGMOID>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -541,11 +576,12 @@ extern "C" int bt_attention_prefill_tcgen05_supports(int head_dim, int page_size
 // q: the step's projections, `q_rows` rows of `q_row_stride` bfloat16; query head h at columns h * head_dim.
 // Packed (kv_table null): k and v point at the first key / value column of the same rows.  Paged: k and v are the
 // pools [pool_pages][n_kv_heads][64][head_dim].  status: optional int that is set to 6 if a bounded wait ran out.
-extern "C" int bt_attention_prefill_tcgen05(const void* q, long long q_rows, long long q_row_stride, const void* k, const void* v,
-                                            long long pool_pages, const int* kv_table, int table_stride, int table_len,
-                                            int page_size, void* out, int* status, const int* seq_start, const int* past_len,
-                                            int n_seqs, int max_new, int n_heads, int n_kv_heads, int head_dim, float scale,
-                                            int causal, int window, cudaStream_t stream) {
+static int run_attention_prefill_tcgen05(const void* q, long long q_rows, long long q_row_stride, const void* k, const void* v,
+                                         long long pool_pages, const int* kv_table, int table_stride, int table_len,
+                                         int page_size, void* out, int* status, const int* seq_start, const int* past_len,
+                                         int n_seqs, int max_new, int n_heads, int n_kv_heads, int head_dim, float scale,
+                                         int causal, int window, int sigmoid, const float* bias, int keep_first,
+                                         cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(bt_attention_prefill_tcgen05_supports(head_dim, page_size > 0 ? page_size : 64),
            "attention_prefill_tcgen05: head_dim %d (page size %d) is not supported", head_dim, page_size);
@@ -575,7 +611,35 @@ extern "C" int bt_attention_prefill_tcgen05(const void* q, long long q_rows, lon
     if (int rc = tensor_map_2d_bf16(&vm, v, rows, head_dim, head_dim, 64)) return rc;
   }
   TaParams p{(__nv_bfloat16*)out, seq_start, past_len, kv_table, table_stride, table_len > 0 ? table_len : 1, status,
-             n_heads, n_kv_heads, k_col, v_col, scale * 1.4426950408889634f, causal, window};
-  if (head_dim == 64) return launch_ta<64>(qm, km, vm, p, n_seqs, max_new, stream);
-  return launch_ta<128>(qm, km, vm, p, n_seqs, max_new, stream);
+             n_heads, n_kv_heads, k_col, v_col, scale * 1.4426950408889634f, causal, window, keep_first, bias};
+  if (sigmoid) {
+    if (head_dim == 64) return launch_ta<64, true>(qm, km, vm, p, n_seqs, max_new, stream);
+    return launch_ta<128, true>(qm, km, vm, p, n_seqs, max_new, stream);
+  }
+  if (head_dim == 64) return launch_ta<64, false>(qm, km, vm, p, n_seqs, max_new, stream);
+  return launch_ta<128, false>(qm, km, vm, p, n_seqs, max_new, stream);
+}
+
+extern "C" int bt_attention_prefill_tcgen05(const void* q, long long q_rows, long long q_row_stride, const void* k, const void* v,
+                                            long long pool_pages, const int* kv_table, int table_stride, int table_len,
+                                            int page_size, void* out, int* status, const int* seq_start, const int* past_len,
+                                            int n_seqs, int max_new, int n_heads, int n_kv_heads, int head_dim, float scale,
+                                            int causal, int window, cudaStream_t stream) {
+  return run_attention_prefill_tcgen05(q, q_rows, q_row_stride, k, v, pool_pages, kv_table, table_stride, table_len, page_size,
+                                       out, status, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale,
+                                       causal, window, 0, nullptr, 0, stream);
+}
+
+// The same for attention whose weights are sigmoid(score * scale + bias[head]), not normalised over the keys; always
+// causal; with a window, positions below `keep_first` stay visible.  Keys and values have the queries' head size.
+extern "C" int bt_sigmoid_attention_tcgen05(const void* q, long long q_rows, long long q_row_stride, const void* k,
+                                            const void* v, long long pool_pages, const int* kv_table, int table_stride,
+                                            int table_len, int page_size, void* out, int* status, const int* seq_start,
+                                            const int* past_len, int n_seqs, int max_new, int n_heads, int n_kv_heads,
+                                            int head_dim, float scale, const float* bias, int window, int keep_first,
+                                            cudaStream_t stream) {
+  BT_CHECK(window >= 0 && keep_first >= 0, "sigmoid_attention_tcgen05: bad window %d or kept positions %d", window, keep_first);
+  return run_attention_prefill_tcgen05(q, q_rows, q_row_stride, k, v, pool_pages, kv_table, table_stride, table_len, page_size,
+                                       out, status, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale,
+                                       1, window, 1, bias, keep_first, stream);
 }

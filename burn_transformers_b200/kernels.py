@@ -1437,6 +1437,37 @@ def sigmoid_attention_prep(proj, q_weight, k_weight, eps, positions, token_seq, 
         c_int(n_kv_heads), c_int(dim), c_int(vdim), c_int(_code(proj.dtype)), _stream()))
 
 
+def sigmoid_attention_tcgen05_supports(dim: int, vdim: int, row_stride: int) -> bool:
+    """Whether sigmoid_attention_tcgen05 takes these sizes: keys and values of one size, 64 or 128 channels, rows of
+    whole 16-byte pieces."""
+    return dim == vdim and row_stride % 8 == 0 and _supports("bt_attention_prefill_tcgen05_supports", dim, PAGE_SIZE)
+
+
+def sigmoid_attention_tcgen05(proj, out, seq_start, past_len, *, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale,
+                              bias=None, window=0, keep_first=0):
+    """sigmoid_attention for sequences that start at position 0, on the tcgen05 tensor cores (bfloat16; scores in tensor
+    memory): `proj` rows hold the prepared queries, keys and values one after another, heads of `head_dim` channels all
+    three; out: [tokens, heads * head_dim].  Scores and sigmoids in 32-bit; a weight enters the value product rounded to
+    bfloat16, the sums are 32-bit."""
+    _need(proj, "proj", torch.bfloat16, (None, (n_heads + 2 * n_kv_heads) * head_dim))
+    _need(out, "out", torch.bfloat16, (None, n_heads * head_dim))
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (n_heads,))
+    if not sigmoid_attention_tcgen05_supports(head_dim, head_dim, proj.shape[1]):
+        raise ShapeError(f"sigmoid_attention_tcgen05: heads of {head_dim} channels in rows of {proj.shape[1]}")
+    if _PROFILE is not None:
+        ctx = float(_PROFILE.context_hint or 0)
+        seen = min(ctx / 2, float(window + keep_first)) if window else ctx / 2
+        _work(4.0 * proj.shape[0] * n_heads * seen * head_dim, 2.0 * proj.shape[0] * (2 * n_heads + 2 * n_kv_heads) * head_dim)
+    q_width, kv_width = n_heads * head_dim, n_kv_heads * head_dim
+    _check(library().bt_sigmoid_attention_tcgen05(
+        _ptr(proj), c_longlong(proj.shape[0]), c_longlong(proj.shape[1]), c_void_p(proj.data_ptr() + q_width * 2),
+        c_void_p(proj.data_ptr() + (q_width + kv_width) * 2), c_longlong(0), c_void_p(0), c_int(0), c_int(0),
+        c_int(PAGE_SIZE), _ptr(out), _ptr(kernel_status(proj.device)), _ptr(seq_start), _ptr(past_len), c_int(n_seqs),
+        c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), _ptr(bias), c_int(window),
+        c_int(keep_first), _stream()))
+
+
 def _grouped_views(q, k, v, out):
     """Strides of q [tokens, heads, dq], k [tokens, kv_heads, dq], v [tokens, kv_heads, dv], out [tokens, heads, dv]."""
     heads, groups, dq, dv = q.shape[1], k.shape[1], q.shape[2], v.shape[2]

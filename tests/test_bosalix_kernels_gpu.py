@@ -112,6 +112,9 @@ def sigmoid_case(rng, heads, groups, dim, vdim, rot_dims, news, pasts, dtype, mi
     (40, 1, 16, 8, 0, 3, 1, False),           # more heads a key head than a block's rows; no rotation
     (2, 2, 72, 130, 72, 0, 0, False),         # no window at all; wide values
     (3, 3, 8, 40, 8, 1, 200, True),           # a window of one token, more kept positions than any sequence is long
+    (8, 2, 64, 64, 32, 100, 7, True),         # keys and values of one size the tcgen05 kernel takes; kept tiles before the window
+    (4, 1, 128, 128, 128, 0, 0, False),       # the same at 128 channels, no window
+    (6, 3, 64, 64, 64, 130, 129, False),      # kept positions that fill a tile of 128 and one more
 ])
 def test_sigmoid_attention_in_prompts_and_in_single_tokens(dtype, tol, heads, groups, dim, vdim, rot_dims, window, keep,
                                                            mixing):
@@ -120,7 +123,7 @@ def test_sigmoid_attention_in_prompts_and_in_single_tokens(dtype, tol, heads, gr
     rng = np.random.default_rng(1)
     scale = 0.7 / math.sqrt(dim)
     bias = rng.standard_normal(heads)
-    for pasts, news in (([0, 0, 0], [130, 1, 65]), ([64, 63, 129, 1], [1, 1, 1, 1]), ([30, 128], [70, 3])):
+    for pasts, news in (([0, 0, 0], [130, 1, 65]), ([64, 63, 129, 1], [1, 1, 1, 1]), ([30, 128], [70, 3]), ([0, 0], [700, 300])):
         proj, other, qw, kw, freqs, lam, pool, table_width, outs = sigmoid_case(rng, heads, groups, dim, vdim, rot_dims, news,
                                                                               pasts, dtype, mixing)
         seqs, counts, rows, seq_start, past, pages, publish = outs[1]
@@ -159,6 +162,14 @@ def test_sigmoid_attention_in_prompts_and_in_single_tokens(dtype, tol, heads, gr
             k = rows[:, heads * dim:(heads + groups) * dim].view(n, groups, dim)
             v = rows[:, (heads + groups) * dim:].view(n, groups, vdim)
             fast = torch.full((n + 1, heads, vdim), 9.0, dtype=dtype, device=DEV)
+            if kernels.sigmoid_attention_tcgen05_supports(dim, vdim, rows.shape[1]):
+                # keys and values of one size of 64 or 128 channels: tcgen05, the scores in tensor memory
+                kernels.sigmoid_attention_tcgen05(rows, fast.view(n + 1, -1), seq_start, past, n_seqs=len(seqs),
+                                                  max_new=max(counts), n_heads=heads, n_kv_heads=groups, head_dim=dim,
+                                                  scale=scale, bias=dev(bias), window=window, keep_first=keep)
+                kernels.check_status(torch.device(DEV))
+                assert rel(host(fast[:n]).reshape(n, -1), host(out[:n])) < tol and bool((fast[n:] == 9.0).all())
+                fast.fill_(9.0)
             takes = kernels.sigmoid_attention_prompt_supports(q, k, v, fast[:n])
             assert takes == (dim % 8 == 0 and vdim % 8 == 0 and vdim <= 128)
             if takes:
