@@ -204,9 +204,10 @@ def _loud_latent(tensors):
 
 @pytest.mark.parametrize("kind", ["sigmoid", "latent"])
 def test_the_window_and_the_kept_positions_are_exact(kind, tmp_path):
-    """One loud key, twice in a sequence: at position 2, among the kept first positions of the sigmoid attention, and at
-    position `window` + 30.  The plain implementation says where its weight ends: `window` positions later and not one
-    sooner or later (for the kept one: never).  Whole prompts, decoding and portions agree with it."""
+    """One loud key, several times in a sequence: at the last kept first position of the sigmoid attention and at the first
+    that is not kept, and at position `window` + 30.  The plain implementation says where its weight ends: `window`
+    positions later and not one sooner or later (for the kept one: never).  Whole prompts, decoding and portions agree
+    with it."""
     if kind == "sigmoid":
         config = bc.sharp(bc.ONLY_SIGMOID, 6.0)
 
@@ -225,24 +226,28 @@ def test_the_window_and_the_kept_positions_are_exact(kind, tmp_path):
     pcfg, pw = bc.load_plain(folder)
     rng = np.random.default_rng(3)
     seq = rng.integers(8, config["vocab"], 3 * window + 20).tolist()
-    seq[2] = 7
-    seq[window + 30] = 7
+    keep = config["layers"][0]["mixer"]["mask"].get("keep_first", 0)
+    early = [keep - 1, keep] if kind == "sigmoid" else [2]      # the last kept position and the first that is not
+    for at in early + [window + 30]:
+        seq[at] = 7
     ref = plain.forward(pcfg, pw, seq)
-    # the plain implementation itself sees the edge: with another token in the loud one's place the logits differ up to the
-    # last position of its window and not at the next; a kept position counts for ever
-    edge = 2 * window + 30
-    other = list(seq)
-    other[window + 30] = 9
-    alt = plain.forward(pcfg, pw, other)
     big = 100 * TOL["float32"] * np.abs(ref).max()
+
+    def without(at):
+        other = list(seq)
+        other[at] = 9
+        return plain.forward(pcfg, pw, other)
+    # the plain implementation itself sees the edges: with another token in a loud one's place the logits differ up to
+    # the last position of its window and not at the next; a kept position counts for ever
+    alt = without(window + 30)
+    edge = 2 * window + 30
     assert np.abs(alt[edge - 1] - ref[edge - 1]).max() > big and np.abs(alt[edge] - ref[edge]).max() < 1e-9
-    other = list(seq)
-    other[2] = 9
-    alt = plain.forward(pcfg, pw, other)
+    alt = without(early[-1])
+    edge = early[-1] + window
+    assert np.abs(alt[edge - 1] - ref[edge - 1]).max() > big and np.abs(alt[edge] - ref[edge]).max() < 1e-9
     if kind == "sigmoid":
-        assert np.abs(alt[-1] - ref[-1]).max() > big
-    else:
-        assert np.abs(alt[window + 1] - ref[window + 1]).max() > big and np.abs(alt[window + 2] - ref[window + 2]).max() < 1e-9
+        alt = without(keep - 1)
+        assert np.abs(alt[-1] - ref[-1]).max() > big and np.abs(alt[keep - 1 + window] - ref[keep - 1 + window]).max() > big
     engine = engine_for(folder, "float32")
     for got in (replay.whole(engine, [seq]), replay.tail_one_by_one(engine, [seq], tail=2 * window + 5),
                 in_portions(engine, [seq], 9)):
