@@ -581,7 +581,7 @@ static int run_attention_prefill_tcgen05(const void* q, long long q_rows, long l
                                          int page_size, void* out, int* status, const int* seq_start, const int* past_len,
                                          int n_seqs, int max_new, int n_heads, int n_kv_heads, int head_dim, float scale,
                                          int causal, int window, int sigmoid, const float* bias, int keep_first,
-                                         cudaStream_t stream) {
+                                         long long pool_row_stride, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(bt_attention_prefill_tcgen05_supports(head_dim, page_size > 0 ? page_size : 64),
            "attention_prefill_tcgen05: head_dim %d (page size %d) is not supported", head_dim, page_size);
@@ -607,8 +607,12 @@ static int run_attention_prefill_tcgen05(const void* q, long long q_rows, long l
   } else {
     BT_CHECK(pool_pages >= 1 && table_len >= 1, "attention_prefill_tcgen05: needs the pools' size and the table's length");
     const unsigned long long rows = (unsigned long long)pool_pages * n_kv_heads * 64;
-    if (int rc = tensor_map_2d_bf16(&km, k, rows, head_dim, head_dim, 64)) return rc;
-    if (int rc = tensor_map_2d_bf16(&vm, v, rows, head_dim, head_dim, 64)) return rc;
+    // (a pool's rows may be longer than a head: keys and values that share a row, one after the other)
+    const unsigned long long row_stride = pool_row_stride > 0 ? (unsigned long long)pool_row_stride : (unsigned long long)head_dim;
+    BT_CHECK(row_stride >= (unsigned long long)head_dim && row_stride % 8 == 0,
+             "attention_prefill_tcgen05: pool rows of %lld elements hold no head of %d", pool_row_stride, head_dim);
+    if (int rc = tensor_map_2d_bf16(&km, k, rows, head_dim, row_stride, 64)) return rc;
+    if (int rc = tensor_map_2d_bf16(&vm, v, rows, head_dim, row_stride, 64)) return rc;
   }
   TaParams p{(__nv_bfloat16*)out, seq_start, past_len, kv_table, table_stride, table_len > 0 ? table_len : 1, status,
              n_heads, n_kv_heads, k_col, v_col, scale * 1.4426950408889634f, causal, window, keep_first, bias};
@@ -627,19 +631,21 @@ extern "C" int bt_attention_prefill_tcgen05(const void* q, long long q_rows, lon
                                             int causal, int window, cudaStream_t stream) {
   return run_attention_prefill_tcgen05(q, q_rows, q_row_stride, k, v, pool_pages, kv_table, table_stride, table_len, page_size,
                                        out, status, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale,
-                                       causal, window, 0, nullptr, 0, stream);
+                                       causal, window, 0, nullptr, 0, 0, stream);
 }
 
 // The same for attention whose weights are sigmoid(score * scale + bias[head]), not normalised over the keys; always
 // causal; with a window, positions below `keep_first` stay visible.  Keys and values have the queries' head size.
+// Paged: k and v point into pools whose rows are `pool_row_stride` elements long (0: head_dim), so that one pool with
+// rows [key | value] serves both.
 extern "C" int bt_sigmoid_attention_tcgen05(const void* q, long long q_rows, long long q_row_stride, const void* k,
                                             const void* v, long long pool_pages, const int* kv_table, int table_stride,
                                             int table_len, int page_size, void* out, int* status, const int* seq_start,
                                             const int* past_len, int n_seqs, int max_new, int n_heads, int n_kv_heads,
                                             int head_dim, float scale, const float* bias, int window, int keep_first,
-                                            cudaStream_t stream) {
+                                            long long pool_row_stride, cudaStream_t stream) {
   BT_CHECK(window >= 0 && keep_first >= 0, "sigmoid_attention_tcgen05: bad window %d or kept positions %d", window, keep_first);
   return run_attention_prefill_tcgen05(q, q_rows, q_row_stride, k, v, pool_pages, kv_table, table_stride, table_len, page_size,
                                        out, status, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale,
-                                       1, window, 1, bias, keep_first, stream);
+                                       1, window, 1, bias, keep_first, pool_row_stride, stream);
 }

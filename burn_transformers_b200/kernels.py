@@ -1444,11 +1444,12 @@ def sigmoid_attention_tcgen05_supports(dim: int, vdim: int, row_stride: int) -> 
 
 
 def sigmoid_attention_tcgen05(proj, out, seq_start, past_len, *, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale,
-                              bias=None, window=0, keep_first=0):
-    """sigmoid_attention for sequences that start at position 0, on the tcgen05 tensor cores (bfloat16; scores in tensor
-    memory): `proj` rows hold the prepared queries, keys and values one after another, heads of `head_dim` channels all
-    three; out: [tokens, heads * head_dim].  Scores and sigmoids in 32-bit; a weight enters the value product rounded to
-    bfloat16, the sums are 32-bit."""
+                              bias=None, window=0, keep_first=0, pool=None, table=None, table_len=0):
+    """sigmoid_attention on the tcgen05 tensor cores (bfloat16; scores in tensor memory): `proj` rows hold the prepared
+    queries, keys and values one after another, heads of `head_dim` channels all three; out: [tokens, heads *
+    head_dim].  Keys and values are the step's own rows (sequences that start at position 0), or, with `pool`
+    [pages, kv_heads, PAGE_SIZE, 2 * head_dim] and `table`, the sequences' pages.  Scores and sigmoids in 32-bit; a
+    weight enters the value product rounded to bfloat16, the sums are 32-bit."""
     _need(proj, "proj", torch.bfloat16, (None, (n_heads + 2 * n_kv_heads) * head_dim))
     _need(out, "out", torch.bfloat16, (None, n_heads * head_dim))
     if bias is not None:
@@ -1460,12 +1461,20 @@ def sigmoid_attention_tcgen05(proj, out, seq_start, past_len, *, n_seqs, max_new
         seen = min(ctx / 2, float(window + keep_first)) if window else ctx / 2
         _work(4.0 * proj.shape[0] * n_heads * seen * head_dim, 2.0 * proj.shape[0] * (2 * n_heads + 2 * n_kv_heads) * head_dim)
     q_width, kv_width = n_heads * head_dim, n_kv_heads * head_dim
+    if table is None:
+        k_ptr = c_void_p(proj.data_ptr() + q_width * 2)
+        v_ptr = c_void_p(proj.data_ptr() + (q_width + kv_width) * 2)
+        t_ptr, t_stride, pages, row = c_void_p(0), 0, 0, 0
+    else:
+        _need(pool, "pool", torch.bfloat16, (None, n_kv_heads, PAGE_SIZE, 2 * head_dim))
+        _need(table, "table", torch.int32)
+        k_ptr, v_ptr = _ptr(pool), c_void_p(pool.data_ptr() + head_dim * 2)
+        t_ptr, t_stride, pages, row = _ptr(table), table.shape[1], pool.shape[0], 2 * head_dim
     _check(library().bt_sigmoid_attention_tcgen05(
-        _ptr(proj), c_longlong(proj.shape[0]), c_longlong(proj.shape[1]), c_void_p(proj.data_ptr() + q_width * 2),
-        c_void_p(proj.data_ptr() + (q_width + kv_width) * 2), c_longlong(0), c_void_p(0), c_int(0), c_int(0),
-        c_int(PAGE_SIZE), _ptr(out), _ptr(kernel_status(proj.device)), _ptr(seq_start), _ptr(past_len), c_int(n_seqs),
-        c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), _ptr(bias), c_int(window),
-        c_int(keep_first), _stream()))
+        _ptr(proj), c_longlong(proj.shape[0]), c_longlong(proj.shape[1]), k_ptr, v_ptr, c_longlong(pages), t_ptr,
+        c_int(t_stride), c_int(table_len), c_int(PAGE_SIZE), _ptr(out), _ptr(kernel_status(proj.device)), _ptr(seq_start),
+        _ptr(past_len), c_int(n_seqs), c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale),
+        _ptr(bias), c_int(window), c_int(keep_first), c_longlong(row), _stream()))
 
 
 def _grouped_views(q, k, v, out):

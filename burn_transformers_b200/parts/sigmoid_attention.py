@@ -36,10 +36,11 @@ class SigmoidAttention(Mixer):
     """
 
     accepts_lazy_norm = False
-    # Prompts of sequences that start at position 0 and bring at least this many tokens take a tensor-core kernel in
-    # bfloat16, which reads keys and values from the step's own rows (csrc/attention_prefill_tcgen05.cu for keys and
-    # values of one size of 64 or 128 channels, csrc/sink_attention_mma.cu for other sizes); everything else (decode
-    # steps, portions that continue a sequence, 32-bit, sizes those kernels do not take) reads the pages.
+    # Steps whose longest run of new tokens is at least this take a tensor-core kernel in bfloat16:
+    # csrc/attention_prefill_tcgen05.cu for keys and values of one size of 64 or 128 channels (fresh prompts over the
+    # step's own rows, portions that continue a sequence over its pages), csrc/sink_attention_mma.cu for fresh prompts
+    # of other sizes; everything else (decode steps, short portions, 32-bit, other sizes) takes the multiply-add kernels
+    # over the pages.
     prompt_from = 48
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float, eps: float, positions,
@@ -115,14 +116,16 @@ class SigmoidAttention(Mixer):
                                        n_kv_heads=self.n_kv_heads, dim=self.dim, vdim=self.vdim,
                                        mix=self.t_mix if v_other is not None else None, v_other=v_other, v_publish=v_publish)
         mixed = ctx.ws.take((n, self.n_heads * self.vdim), dtype)
-        if dtype == torch.bfloat16 and ctx.fresh and not ctx.is_decode and ctx.max_new >= self.prompt_from:
-            # fresh prompts: keys and values are the step's own rows, the sums run on tensor cores: tcgen05 with the
-            # scores in tensor memory where keys and values have one size the kernel is built for, else `mma.sync`
+        if dtype == torch.bfloat16 and not ctx.is_decode and ctx.max_new >= self.prompt_from:
+            # prompts and their portions on tensor cores: tcgen05 with the scores in tensor memory where keys and values
+            # have one size the kernel is built for (fresh prompts attend over the step's own rows, portions that
+            # continue a sequence over its pages); else, for fresh prompts, `mma.sync`
             if kernels.sigmoid_attention_tcgen05_supports(self.dim, self.vdim, self.proj_width):
+                paged = {} if ctx.fresh else {"pool": k_pool, "table": table, "table_len": group.table_len}
                 kernels.sigmoid_attention_tcgen05(proj, mixed, ctx.seq_start, ctx.past_len, n_seqs=ctx.n_seqs,
                                                   max_new=ctx.max_new, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
                                                   head_dim=self.dim, scale=self.scale, bias=self.t_bias,
-                                                  window=self.window or 0, keep_first=self.keep_first)
+                                                  window=self.window or 0, keep_first=self.keep_first, **paged)
                 linear(ctx, mixed, self.t_out_weight, self.t_out_bias, residual, m=n, residual=residual, w_is_nk=True)
                 ctx.ws.release(mark)
                 return
@@ -130,7 +133,7 @@ class SigmoidAttention(Mixer):
             k = proj[:, self.q_width:self.q_width + self.k_width].view(n, self.n_kv_heads, self.dim)
             v = proj[:, self.q_width + self.k_width:].view(n, self.n_kv_heads, self.vdim)
             out = mixed.view(n, self.n_heads, self.vdim)
-            if kernels.sigmoid_attention_prompt_supports(q, k, v, out):
+            if ctx.fresh and kernels.sigmoid_attention_prompt_supports(q, k, v, out):
                 kernels.sigmoid_attention_prompt(q, k, v, out, ctx.seq_start, n_seqs=ctx.n_seqs, max_new=ctx.max_new,
                                                  scale=self.scale, bias=self.t_bias, window=self.window or 0,
                                                  keep_first=self.keep_first)

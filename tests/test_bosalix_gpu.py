@@ -90,8 +90,8 @@ def test_prompts_in_portions(case, dtype, size):
     """The pages, the row a token shift keeps, and the positions carry a sequence from one portion to the next; the
     values a later layer blends in are those of the portion's own tokens."""
     name, folder, seqs, ref = case
-    if name not in ("mixed", "value_mixing") and size in (3, 15, 70):
-        pytest.skip("the full set of portion sizes runs on two configurations")
+    if name not in ("mixed", "value_mixing", "large") and size in (3, 15, 70):
+        pytest.skip("the full set of portion sizes runs on three configurations")
     engine = engine_for(folder, dtype)
     assert engine.cache.max_continued_run is None
     got = in_portions(engine, seqs, size)

@@ -123,7 +123,7 @@ def test_sigmoid_attention_in_prompts_and_in_single_tokens(dtype, tol, heads, gr
     rng = np.random.default_rng(1)
     scale = 0.7 / math.sqrt(dim)
     bias = rng.standard_normal(heads)
-    for pasts, news in (([0, 0, 0], [130, 1, 65]), ([64, 63, 129, 1], [1, 1, 1, 1]), ([30, 128], [70, 3]), ([0, 0], [700, 300])):
+    for pasts, news in (([0, 0, 0], [130, 1, 65]), ([64, 63, 129, 1], [1, 1, 1, 1]), ([30, 128], [70, 3]), ([0, 0], [700, 300]), ([200, 0, 5], [300, 130, 64])):
         proj, other, qw, kw, freqs, lam, pool, table_width, outs = sigmoid_case(rng, heads, groups, dim, vdim, rot_dims, news,
                                                                               pasts, dtype, mixing)
         seqs, counts, rows, seq_start, past, pages, publish = outs[1]
@@ -156,6 +156,14 @@ def test_sigmoid_attention_in_prompts_and_in_single_tokens(dtype, tol, heads, gr
             want = want[pasts[s]:].reshape(count, -1)
             assert rel(host(out[at:at + count]), want) < tol, (pasts, news, s)
             at += count
+        if dtype == torch.bfloat16 and any(pasts) and kernels.sigmoid_attention_tcgen05_supports(dim, vdim, rows.shape[1]):
+            # portions that continue a sequence (and single tokens) through the tcgen05 kernel over the pages
+            fast = torch.full((n + 1, heads * vdim), 9.0, dtype=dtype, device=DEV)
+            kernels.sigmoid_attention_tcgen05(rows, fast, seq_start, past, n_seqs=len(seqs), max_new=max(counts),
+                                              n_heads=heads, n_kv_heads=groups, head_dim=dim, scale=scale, bias=dev(bias),
+                                              window=window, keep_first=keep, pool=pool, table=pages, table_len=table_width)
+            kernels.check_status(torch.device(DEV))
+            assert rel(host(fast[:n]), host(out[:n])) < tol and bool((fast[n:] == 9.0).all())
         if dtype == torch.bfloat16 and not any(pasts):
             # the same prompts through the tensor-core kernel that reads keys and values from the step's own rows
             q = rows[:, :heads * dim].view(n, heads, dim)
