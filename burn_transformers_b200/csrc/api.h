@@ -205,7 +205,8 @@ int bt_moe_expert(int first, const void* a, long long a_row_stride, const void* 
                   const int* tile_first, const int* order, const float* pair_weight, int pairs, int E, int top, int K,
                   int N, int act, float limit, int tensor_cores, int dtype, cudaStream_t stream);
 int bt_moe_combine(const float* part, const int* place, float* stream_rows, long long n_tokens, int top, int width,
-                   const int* ids, const float* weights, const float* input, int n_stored, cudaStream_t stream);
+                   const int* ids, const float* weights, const float* input, int n_stored, int store,
+                   cudaStream_t stream);
 int bt_add_vector(float* x, const float* vec, long long n_rows, int width, cudaStream_t stream);
 int bt_add_rows(float* x, const float* a, const float* b, const float* c, long long n, cudaStream_t stream);
 

@@ -528,12 +528,12 @@ moe_expert_few_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* 
   }
 }
 
-// stream[t, c] += sum_j part[place[t * top + j], c]; a pair whose expert is `n_stored` or more adds weight * input[t, c]
-// instead (`ids` null: every pair has a row in `part`)
+// stream[t, c] += sum_j part[place[t * top + j], c] (`store`: =, the rows are written, not added to); a pair whose expert
+// is `n_stored` or more adds weight * input[t, c] instead (`ids` null: every pair has a row in `part`)
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ part, const int* __restrict__ place, float* __restrict__ stream,
                    long long n_tokens, int top, int width, const int* __restrict__ ids, const float* __restrict__ weights,
-                   const float* __restrict__ input, int n_stored) {
+                   const float* __restrict__ input, int n_stored, int store) {
   pdl_trigger();
   pdl_wait();
   const long long total = n_tokens * width;
@@ -545,7 +545,7 @@ moe_combine_kernel(const float* __restrict__ part, const int* __restrict__ place
       if (ids != nullptr && ids[t * top + j] >= n_stored) sum = fmaf(weights[t * top + j], input[i], sum);
       else sum += part[(long long)place[t * top + j] * width + c];
     }
-    stream[i] += sum;
+    stream[i] = store ? sum : stream[i] + sum;      // (`store`: the rows hold nothing yet)
   }
 }
 
@@ -663,7 +663,7 @@ extern "C" int bt_moe_expert(int first, const void* a, long long a_row_stride, c
 
 extern "C" int bt_moe_combine(const float* part, const int* place, float* stream_rows, long long n_tokens, int top,
                               int width, const int* ids, const float* weights, const float* input, int n_stored,
-                              cudaStream_t stream) {
+                              int store, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_tokens >= 0 && top > 0 && width > 0, "moe_combine: bad sizes");
   BT_CHECK(ids == nullptr || (weights != nullptr && input != nullptr), "moe_combine: pairs that hand the input on need weights and the input");
@@ -671,6 +671,6 @@ extern "C" int bt_moe_combine(const float* part, const int* place, float* stream
   const long long total = n_tokens * width;
   const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
   BT_PDL_OK("moe_combine", launch_pdl(moe_combine_kernel, dim3(blocks), dim3(256), 0, stream, 1, part, place, stream_rows,
-                                      n_tokens, top, width, ids, weights, input, n_stored));
+                                      n_tokens, top, width, ids, weights, input, n_stored, store));
   return 0;
 }

@@ -1006,10 +1006,12 @@ def moe_expert(first: bool, a, w, out, offsets, tile_first, order, pair_weight, 
                                    c_int(1 if tensor_cores else 0), c_int(_code(a.dtype)), _stream()))
 
 
-def moe_combine(part, place, stream_rows, *, n_tokens, top, ids=None, weights=None, identity_input=None, n_stored=0):
+def moe_combine(part, place, stream_rows, *, n_tokens, top, ids=None, weights=None, identity_input=None, n_stored=0,
+                store=False):
     """stream_rows[t] += sum over the token's `top` pairs of part[place[t * top + j]], in that order (32-bit).  With `ids`
     ([tokens, top], the pairs' experts), a pair whose expert is `n_stored` or more adds weights[t, j] * identity_input[t]
-    instead (an expert without tensors that hands its input on; identity_input: contiguous 32-bit [tokens, width])."""
+    instead (an expert without tensors that hands its input on; identity_input: contiguous 32-bit [tokens, width]).
+    `store`: the sums are written into stream_rows instead of added (rows that hold nothing yet)."""
     width = stream_rows.shape[1]
     if ids is not None:
         _need(ids, "ids", torch.int32, (None, top))
@@ -1025,7 +1027,7 @@ def moe_combine(part, place, stream_rows, *, n_tokens, top, ids=None, weights=No
     _work(0.0, 4.0 * n_tokens * width * (top + 2))
     _check(library().bt_moe_combine(_ptr(part), _ptr(place), _ptr(stream_rows), c_longlong(n_tokens), c_int(top),
                                     c_int(width), _ptr(ids), _ptr(weights), _ptr(identity_input), c_int(n_stored),
-                                    _stream()))
+                                    c_int(1 if store else 0), _stream()))
 
 
 def scale_(x, factor: float):

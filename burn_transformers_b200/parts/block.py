@@ -210,9 +210,9 @@ class OutputNormBlock(Block):
     one number for the whole model.  The sublayers read the stream itself (rounded to the products' type); with a
     `shift` (parts.token_shift.TokenShift) the mixer reads every row blended with the row of the token before it.
 
-    A sublayer adds into a zeroed 32-bit buffer; one kernel (csrc/rowwise.cu: rmsnorm_add) norms the buffer, adds m
-    times the result to the stream and, where the feed-forward follows, writes the new row in the products' type for
-    it in the same pass.  Both norms are RMS norms of one eps."""
+    A sublayer leaves its result in a 32-bit buffer (zeroed first for parts that can only add); one kernel
+    (csrc/rowwise.cu: rmsnorm_add) norms the buffer, adds m times the result to the stream and, where the feed-forward
+    follows, writes the new row in the products' type for it in the same pass.  Both norms are RMS norms of one eps."""
 
     def __init__(self, mixer: Mixer, norm1: Norm, feed_forward: FeedForward | None = None, norm2: Norm | None = None,
                  *, scale: float = 1.0, shift=None):
@@ -261,8 +261,12 @@ class OutputNormBlock(Block):
             rows[:n].copy_(residual[:n])
             x = rows
         inner = ctx.ws.mark()
-        branch.zero_()
-        self.mixer.forward(ctx, x, branch, entry, owns_cache)
+        # (a part that can store its result instead of adding it needs no zeroed buffer: one launch less a sublayer)
+        if getattr(self.mixer, "can_store", False):
+            self.mixer.forward(ctx, x, branch, entry, owns_cache, store=True)
+        else:
+            branch.zero_()
+            self.mixer.forward(ctx, x, branch, entry, owns_cache)
         ctx.ws.release(inner)
         if self.feed_forward is None:
             kernels.rmsnorm_add(branch, self.norm1.t_weight, residual, self.norm1.eps, n_rows=n, factor=self.scale)
@@ -272,10 +276,11 @@ class OutputNormBlock(Block):
         kernels.rmsnorm_add(branch, self.norm1.t_weight, residual, self.norm1.eps, n_rows=n, factor=self.scale,
                             next_out=None if exact else rows)
         x = residual if exact else rows
-        branch.zero_()
-        if getattr(self.feed_forward, "wants_x32", False):
-            self.feed_forward.forward(ctx, x, branch, x32=residual)
+        more = {"x32": residual} if getattr(self.feed_forward, "wants_x32", False) else {}
+        if getattr(self.feed_forward, "can_store", False) and getattr(self.feed_forward, "shared", None) is None:
+            self.feed_forward.forward(ctx, x, branch, store=True, **more)
         else:
-            self.feed_forward.forward(ctx, x, branch)
+            branch.zero_()
+            self.feed_forward.forward(ctx, x, branch, **more)
         kernels.rmsnorm_add(branch, self.norm2.t_weight, residual, self.norm2.eps, n_rows=n, factor=self.scale)
         ctx.ws.release(mark)

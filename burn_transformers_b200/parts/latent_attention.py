@@ -116,7 +116,10 @@ class LatentAttention(Mixer):
         span = ctx.ctx_bound if self.window is None else min(ctx.ctx_bound, self.window + 64)
         return int(max(1, min(by_fill, -(-span // 32), 64)))
 
-    def forward(self, ctx, x, residual, entry, owns_cache=True):
+    # `forward(..., store=True)` writes the result into `residual` instead of adding it (rows that hold nothing yet)
+    can_store = True
+
+    def forward(self, ctx, x, residual, entry, owns_cache=True, store=False):
         if getattr(ctx, "program", None) is not None:
             from ..engine.program import ProgramUnsupported
             raise ProgramUnsupported("latent attention has no phase in the fused step")
@@ -168,7 +171,7 @@ class LatentAttention(Mixer):
             kernels.latent_decode_finish(self.uv_heads, mixed, n_tokens=n, n_splits=splits, scratch=scratch,
                                          mixed_latent=mixed_latent,
                                          gate=proj[:, gate_off:latent_off] if self.has_gate else None)
-            linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)
+            linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=None if store else residual, w_is_nk=True)
             ctx.ws.release(mark)
             return
         if self.owns_latent:
@@ -196,7 +199,7 @@ class LatentAttention(Mixer):
                 kernels.sink_attention(q_heads, keys, values, mixed_heads, ctx.seq_start, n_seqs=ctx.n_seqs,
                                        max_new=ctx.max_new, scale=self.scale,
                                        sink=self.t_sink if self.has_sink else None, gate=gate, window=window)
-                linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)
+                linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=None if store else residual, w_is_nk=True)
                 ctx.ws.release(mark)
                 return
         # the queries as the latent rows meet them: per head [W_uk^T q_plain | q_rot turned]
@@ -218,5 +221,5 @@ class LatentAttention(Mixer):
         mixed = ctx.ws.take((n, self.mixed_width), dtype)
         kernels.head_linear(mixed_latent.view(n, heads, rank), self.uv_heads, mixed.view(n, heads, self.vdim), n_tokens=n,
                             gate=gate)
-        linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)
+        linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=None if store else residual, w_is_nk=True)
         ctx.ws.release(mark)

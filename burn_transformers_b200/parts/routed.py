@@ -90,12 +90,15 @@ class RoutedFeedForward(FeedForward):
         """Whether `forward` needs the 32-bit rows beside the rounded ones (experts that hand their input on)."""
         return self.identity > 0
 
-    def forward(self, ctx, x, residual, x32=None):
-        self.forward_routed(ctx, x, residual, x32)
+    # `forward(..., store=True)` writes the result into `residual` instead of adding it (rows that hold nothing yet)
+    can_store = True
+
+    def forward(self, ctx, x, residual, x32=None, store=False):
+        self.forward_routed(ctx, x, residual, x32, store)
         if self.shared is not None:
             self.shared.forward(ctx, x, residual)
 
-    def forward_routed(self, ctx, x, residual, x32=None):
+    def forward_routed(self, ctx, x, residual, x32=None, store=False):
         """The routed experts alone (the shared one is a feed-forward of its own and may run beside them)."""
         if getattr(ctx, "program", None) is not None:
             from ..engine.program import ProgramUnsupported
@@ -126,7 +129,7 @@ class RoutedFeedForward(FeedForward):
         kernels.moe_expert(False, hidden, self.w_out, part, offsets, tile_first, order, weights, pairs=pairs, top=top)
         if self.identity:
             kernels.moe_combine(part, place, residual, n_tokens=n, top=top, ids=ids, weights=weights, identity_input=x32,
-                                n_stored=e)
+                                n_stored=e, store=store)
         else:
-            kernels.moe_combine(part, place, residual, n_tokens=n, top=top)
+            kernels.moe_combine(part, place, residual, n_tokens=n, top=top, store=store)
         ctx.ws.release(mark)

@@ -86,7 +86,10 @@ class SigmoidAttention(Mixer):
     def cache_need(self):
         return CacheNeed(kv=KvSpec(self.n_kv_heads, self.dim + self.vdim, None, has_values=False))
 
-    def forward(self, ctx, x, residual, entry, owns_cache=True):
+    # `forward(..., store=True)` writes the result into `residual` instead of adding it (rows that hold nothing yet)
+    can_store = True
+
+    def forward(self, ctx, x, residual, entry, owns_cache=True, store=False):
         if getattr(ctx, "program", None) is not None:
             from ..engine.program import ProgramUnsupported
             raise ProgramUnsupported("sigmoid attention has no phase in the fused step")
@@ -126,7 +129,8 @@ class SigmoidAttention(Mixer):
                                                   max_new=ctx.max_new, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
                                                   head_dim=self.dim, scale=self.scale, bias=self.t_bias,
                                                   window=self.window or 0, keep_first=self.keep_first, **paged)
-                linear(ctx, mixed, self.t_out_weight, self.t_out_bias, residual, m=n, residual=residual, w_is_nk=True)
+                linear(ctx, mixed, self.t_out_weight, self.t_out_bias, residual, m=n, residual=None if store else residual,
+                       w_is_nk=True)
                 ctx.ws.release(mark)
                 return
             q = proj[:, :self.q_width].view(n, self.n_heads, self.dim)
@@ -137,12 +141,14 @@ class SigmoidAttention(Mixer):
                 kernels.sigmoid_attention_prompt(q, k, v, out, ctx.seq_start, n_seqs=ctx.n_seqs, max_new=ctx.max_new,
                                                  scale=self.scale, bias=self.t_bias, window=self.window or 0,
                                                  keep_first=self.keep_first)
-                linear(ctx, mixed, self.t_out_weight, self.t_out_bias, residual, m=n, residual=residual, w_is_nk=True)
+                linear(ctx, mixed, self.t_out_weight, self.t_out_bias, residual, m=n, residual=None if store else residual,
+                       w_is_nk=True)
                 ctx.ws.release(mark)
                 return
         kernels.sigmoid_attention(proj, mixed, k_pool, table, group.table_len, ctx.seq_start, ctx.past_len,
                                   n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=self.n_heads,
                                   n_kv_heads=self.n_kv_heads, dim=self.dim, vdim=self.vdim, scale=self.scale,
                                   bias=self.t_bias, window=self.window or 0, keep_first=self.keep_first)
-        linear(ctx, mixed, self.t_out_weight, self.t_out_bias, residual, m=n, residual=residual, w_is_nk=True)
+        linear(ctx, mixed, self.t_out_weight, self.t_out_bias, residual, m=n, residual=None if store else residual,
+                       w_is_nk=True)
         ctx.ws.release(mark)
