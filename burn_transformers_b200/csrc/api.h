@@ -38,8 +38,8 @@ int bt_attention_prefill_tcgen05_supports(int head_dim, int page_size);
 int bt_sigmoid_attention_tcgen05(const void* q, long long q_rows, long long q_row_stride, const void* k, const void* v,
                                  long long pool_pages, const int* kv_table, int table_stride, int table_len, int page_size,
                                  void* out, int* status, const int* seq_start, const int* past_len, int n_seqs, int max_new,
-                                 int n_heads, int n_kv_heads, int head_dim, float scale, const float* bias, int window,
-                                 int keep_first, long long pool_row_stride, cudaStream_t stream);
+                                 int n_heads, int n_kv_heads, int head_dim, int v_dim, float scale, const float* bias,
+                                 int window, int keep_first, long long pool_row_stride, cudaStream_t stream);
 int bt_attention_prefill_tcgen05(const void* q, long long q_rows, long long q_row_stride, const void* k, const void* v,
                                  long long pool_pages, const int* kv_table, int table_stride, int table_len, int page_size,
                                  void* out, int* status, const int* seq_start, const int* past_len, int n_seqs, int max_new,

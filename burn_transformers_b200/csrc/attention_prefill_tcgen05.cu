@@ -44,7 +44,7 @@ constexpr int TA_WAIT_LIMIT = 1 << 22;
 constexpr int TA_BOX_BYTES = 64 * 128;            // a 64-row x 64-column bfloat16 box
 
 struct TaParams {
-  __nv_bfloat16* out;          // [tokens, n_heads * HD]
+  __nv_bfloat16* out;          // [tokens, n_heads * HV]
   const int* seq_start;
   const int* past_len;
   const int* table;            // null: keys and values are rows of the projections
@@ -144,33 +144,37 @@ __device__ __forceinline__ unsigned ta_pack(float lo, float hi) {
 __device__ __forceinline__ void ta_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void ta_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 
-// Tensor memory of a block: two S accumulators (2 x 128 columns) and two P V accumulators (2 x HD columns), at most
+// Tensor memory of a block: two S accumulators (2 x 128 columns) and two P V accumulators (2 x HV columns), at most
 // 512 columns: the whole of a multiprocessor's, which one block has to itself.
 constexpr int TA_TMEM_COLS = 512;
 
 // Shared memory (the dynamic region, which must start on a 1024-byte boundary):
 //   Q      [HD / 64][128 rows][128 bytes]
-//   K, V   [stage][HD / 64][128 keys][128 bytes] each, two stages
+//   K      [stage][HD / 64][128 keys][128 bytes], two stages;  V the same with HV, the values' head size (HD for the
+//          softmax attention; the sigmoid attention's keys and values may differ in size)
 //   P      [tile parity][2][128 rows][128 bytes]    (keys 0-63 | 64-127 of the tile)
 //   the row maxima the two threads of a row exchange [tile parity][2 halves][128] (at the end: their sums)
 //   barriers, the tensor-memory address, the failure flag
-template <int HD>
+template <int HD, int HV>
 constexpr size_t ta_smem_bytes() {
-  return (size_t)(HD / 64) * 2 * TA_BOX_BYTES * (1 + 2 * TA_STAGES) + 2 * 2 * 2 * TA_BOX_BYTES + 4 * 128 * 4 + 256;
+  return (size_t)(HD / 64) * 2 * TA_BOX_BYTES * (1 + TA_STAGES) + (size_t)(HV / 64) * 2 * TA_BOX_BYTES * TA_STAGES +
+         2 * 2 * 2 * TA_BOX_BYTES + 4 * 128 * 4 + 256;
 }
 
-template <int HD, bool SIGMOID>
+template <int HD, int HV, bool SIGMOID>
 __global__ void __launch_bounds__(TA_THREADS, 1)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                                  const __grid_constant__ CUtensorMap v_map, TaParams p) {
-  constexpr int CB = HD / 64;                              // 64-column boxes per row of a head
-  constexpr int TILE_BYTES = CB * 2 * TA_BOX_BYTES;        // 128 rows of a head
-  constexpr int HH = HD / 2;                               // output channels of one of the two threads of a row
+  constexpr int CB = HD / 64, CBV = HV / 64;               // 64-column boxes per row of a query or key head, of a value head
+  constexpr int TILE_BYTES = CB * 2 * TA_BOX_BYTES;        // 128 rows of a query or key head
+  constexpr int TILE_V = CBV * 2 * TA_BOX_BYTES;           // 128 rows of a value head
+  constexpr int HH = HV / 2;                               // output channels of one of the two threads of a row
+  static_assert(2 * TA_BK + 2 * HV <= TA_TMEM_COLS, "the accumulators outgrow the tensor memory");
   extern __shared__ __align__(1024) unsigned char ta_raw[];
   unsigned char* Qs = ta_raw;
   unsigned char* Ks = Qs + TILE_BYTES;                     // [stage]
   unsigned char* Vs = Ks + TA_STAGES * TILE_BYTES;         // [stage]
-  unsigned char* Ps = Vs + TA_STAGES * TILE_BYTES;                         // [tile parity][2 boxes]
+  unsigned char* Ps = Vs + TA_STAGES * TILE_V;                             // [tile parity][2 boxes]
   float* x_max = reinterpret_cast<float*>(Ps + 2 * 2 * 2 * TA_BOX_BYTES);  // [tile parity][half][row]
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(x_max + 4 * 128);
   unsigned long long* q_full = bars;                       // 1
@@ -262,18 +266,18 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         } else {
           row = t0 + kt * TA_BK + h * 64;
           col_k = p.k_col + kv_head * HD;
-          col_v = p.v_col + kv_head * HD;
+          col_v = p.v_col + kv_head * HV;
         }
       };
       auto load = [&](int it, bool values) {
         const int s = it % TA_STAGES;
         unsigned long long* bar = values ? &v_full[s] : &k_full[s];
-        unsigned char* dst = (values ? Vs : Ks) + s * TILE_BYTES;
-        ta_bar_expect(bar, TILE_BYTES);
+        unsigned char* dst = values ? Vs + s * TILE_V : Ks + s * TILE_BYTES;
+        ta_bar_expect(bar, values ? TILE_V : TILE_BYTES);
         for (int h = 0; h < 2; ++h) {
           int row, col_k, col_v;
           where(it, h, row, col_k, col_v);
-          for (int cb = 0; cb < CB; ++cb)
+          for (int cb = 0; cb < (values ? CBV : CB); ++cb)
             ta_tma(dst + cb * 2 * TA_BOX_BYTES + h * TA_BOX_BYTES, values ? &v_map : &k_map, (values ? col_v : col_k) + cb * 64, row, bar);
         }
       };
@@ -301,9 +305,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
     if (lane == 0) {
       // ---- issuer ----
       // instruction descriptors: 32-bit accumulator, bfloat16 operands, M = 128; S: N = 128, both K-major;
-      // P V: N = HD, the second operand MN-major
+      // P V: N = HV, the second operand MN-major
       const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TA_BK >> 3) << 17) | ((unsigned)(TA_BQ >> 4) << 24);
-      const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((unsigned)(TA_BQ >> 4) << 24);
+      const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HV >> 3) << 17) | ((unsigned)(TA_BQ >> 4) << 24);
       // operand descriptors, made once: Q and K per 16 channels, P per 16 keys, V per 16 keys (and stage)
       unsigned long long dq[HD / 16], dk[TA_STAGES][HD / 16], dp[TA_BK / 16], dv[TA_STAGES][TA_BK / 16];
 #pragma unroll
@@ -317,7 +321,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         dp[j] = ta_desc(Ps + (j / 4) * 2 * TA_BOX_BYTES, 16) + 2ull * (j % 4);      // (the second P tile: 32 KB further)
         // 16 keys further: 16 rows of 128 bytes; the next 64 channels: a whole 128-row box further
 #pragma unroll
-        for (int s = 0; s < TA_STAGES; ++s) dv[s][j] = ta_desc(Vs + s * TILE_BYTES + j * 16 * 128, 2 * TA_BOX_BYTES);
+        for (int s = 0; s < TA_STAGES; ++s) dv[s][j] = ta_desc(Vs + s * TILE_V + j * 16 * 128, 2 * TA_BOX_BYTES);
       }
       // S of tile `it` = Q K^T into accumulator it % 2, when the tile's keys have landed.  (The accumulator is free:
       // the softmax warps had read tile it - 2's before they announced its P.)
@@ -356,7 +360,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
         } else {
 #pragma unroll
           for (int j = 0; j < TA_BK / 16; ++j)
-            ta_mma(tmem_o + (unsigned)HD, dp[j] + (unsigned long long)((2 * 2 * TA_BOX_BYTES) >> 4), dv[1][j], idesc_o, j > 0 ? 1u : 0u);
+            ta_mma(tmem_o + (unsigned)HV, dp[j] + (unsigned long long)((2 * 2 * TA_BOX_BYTES) >> 4), dv[1][j], idesc_o, j > 0 ? 1u : 0u);
         }
         ta_commit(&o_full[it & 1]);
         ta_commit(&v_empty[s]);
@@ -379,7 +383,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
     // adds the P V of tile `t` (accumulator t % 2) to this thread's channels and hands the accumulator back
     auto take_o = [&](int t) {
       unsigned a[32], b[32];
-      const unsigned addr = tmem_o + (unsigned)((t & 1) * HD) + lane_base + (unsigned)(half * HH);
+      const unsigned addr = tmem_o + (unsigned)((t & 1) * HV) + lane_base + (unsigned)(half * HH);
       if constexpr (HH == 32) {
         ta_ld32_issue(addr, a);
         ta_ld32_issue(addr, b);
@@ -527,7 +531,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
     if (!ok) *failed = 1;
     if (ok && r < nq) {
       const float inv = SIGMOID ? 1.f : (l > 0.f ? 1.f / l : 0.f);
-      __nv_bfloat16* dst = p.out + (long long)(t0 + q0 + r) * ((long long)p.n_heads * HD) + head * HD + half * HH;
+      __nv_bfloat16* dst = p.out + (long long)(t0 + q0 + r) * ((long long)p.n_heads * HV) + head * HV + half * HH;
 #pragma unroll
       for (int c = 0; c < HH; c += 8) {
         uint4 x;
@@ -548,11 +552,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, cons
   if (threadIdx.x == 0 && *failed && p.status) atomicExch(p.status, 6);
 }
 
-template <int HD, bool SIGMOID>
+template <int HD, int HV, bool SIGMOID>
 static int launch_ta(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const TaParams& p, int n_seqs, int max_new,
                      cudaStream_t stream) {
-  constexpr size_t smem = ta_smem_bytes<HD>();
-  auto kern = attention_prefill_tcgen05_kernel<HD, SIGMOID>;
+  constexpr size_t smem = ta_smem_bytes<HD, HV>();
+  auto kern = attention_prefill_tcgen05_kernel<HD, HV, SIGMOID>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -581,7 +585,7 @@ static int run_attention_prefill_tcgen05(const void* q, long long q_rows, long l
                                          int page_size, void* out, int* status, const int* seq_start, const int* past_len,
                                          int n_seqs, int max_new, int n_heads, int n_kv_heads, int head_dim, float scale,
                                          int causal, int window, int sigmoid, const float* bias, int keep_first,
-                                         long long pool_row_stride, cudaStream_t stream) {
+                                         long long pool_row_stride, int v_dim, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(bt_attention_prefill_tcgen05_supports(head_dim, page_size > 0 ? page_size : 64),
            "attention_prefill_tcgen05: head_dim %d (page size %d) is not supported", head_dim, page_size);
@@ -597,7 +601,7 @@ static int run_attention_prefill_tcgen05(const void* q, long long q_rows, long l
   int k_col = 0, v_col = 0;
   if (kv_table == nullptr) {
     const long long ko = (const __nv_bfloat16*)k - (const __nv_bfloat16*)q, vo = (const __nv_bfloat16*)v - (const __nv_bfloat16*)q;
-    BT_CHECK(ko >= 0 && vo >= 0 && ko + (long long)n_kv_heads * head_dim <= q_row_stride && vo + (long long)n_kv_heads * head_dim <= q_row_stride &&
+    BT_CHECK(ko >= 0 && vo >= 0 && ko + (long long)n_kv_heads * head_dim <= q_row_stride && vo + (long long)n_kv_heads * v_dim <= q_row_stride &&
                  ko % 8 == 0 && vo % 8 == 0,
              "attention_prefill_tcgen05: packed keys and values must be 16-byte aligned columns of the query rows");
     k_col = (int)ko;
@@ -609,19 +613,23 @@ static int run_attention_prefill_tcgen05(const void* q, long long q_rows, long l
     const unsigned long long rows = (unsigned long long)pool_pages * n_kv_heads * 64;
     // (a pool's rows may be longer than a head: keys and values that share a row, one after the other)
     const unsigned long long row_stride = pool_row_stride > 0 ? (unsigned long long)pool_row_stride : (unsigned long long)head_dim;
-    BT_CHECK(row_stride >= (unsigned long long)head_dim && row_stride % 8 == 0,
+    BT_CHECK(row_stride >= (unsigned long long)head_dim && row_stride >= (unsigned long long)v_dim && row_stride % 8 == 0,
              "attention_prefill_tcgen05: pool rows of %lld elements hold no head of %d", pool_row_stride, head_dim);
     if (int rc = tensor_map_2d_bf16(&km, k, rows, head_dim, row_stride, 64)) return rc;
-    if (int rc = tensor_map_2d_bf16(&vm, v, rows, head_dim, row_stride, 64)) return rc;
+    if (int rc = tensor_map_2d_bf16(&vm, v, rows, v_dim, row_stride, 64)) return rc;
   }
   TaParams p{(__nv_bfloat16*)out, seq_start, past_len, kv_table, table_stride, table_len > 0 ? table_len : 1, status,
              n_heads, n_kv_heads, k_col, v_col, scale * 1.4426950408889634f, causal, window, keep_first, bias};
+  BT_CHECK((v_dim == 64 || v_dim == 128) && (sigmoid || v_dim == head_dim),
+           "attention_prefill_tcgen05: values of %d channels beside keys of %d are not supported", v_dim, head_dim);
   if (sigmoid) {
-    if (head_dim == 64) return launch_ta<64, true>(qm, km, vm, p, n_seqs, max_new, stream);
-    return launch_ta<128, true>(qm, km, vm, p, n_seqs, max_new, stream);
+    if (head_dim == 64 && v_dim == 64) return launch_ta<64, 64, true>(qm, km, vm, p, n_seqs, max_new, stream);
+    if (head_dim == 64) return launch_ta<64, 128, true>(qm, km, vm, p, n_seqs, max_new, stream);
+    if (v_dim == 64) return launch_ta<128, 64, true>(qm, km, vm, p, n_seqs, max_new, stream);
+    return launch_ta<128, 128, true>(qm, km, vm, p, n_seqs, max_new, stream);
   }
-  if (head_dim == 64) return launch_ta<64, false>(qm, km, vm, p, n_seqs, max_new, stream);
-  return launch_ta<128, false>(qm, km, vm, p, n_seqs, max_new, stream);
+  if (head_dim == 64) return launch_ta<64, 64, false>(qm, km, vm, p, n_seqs, max_new, stream);
+  return launch_ta<128, 128, false>(qm, km, vm, p, n_seqs, max_new, stream);
 }
 
 extern "C" int bt_attention_prefill_tcgen05(const void* q, long long q_rows, long long q_row_stride, const void* k, const void* v,
@@ -631,21 +639,22 @@ extern "C" int bt_attention_prefill_tcgen05(const void* q, long long q_rows, lon
                                             int causal, int window, cudaStream_t stream) {
   return run_attention_prefill_tcgen05(q, q_rows, q_row_stride, k, v, pool_pages, kv_table, table_stride, table_len, page_size,
                                        out, status, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale,
-                                       causal, window, 0, nullptr, 0, 0, stream);
+                                       causal, window, 0, nullptr, 0, 0, head_dim, stream);
 }
 
 // The same for attention whose weights are sigmoid(score * scale + bias[head]), not normalised over the keys; always
-// causal; with a window, positions below `keep_first` stay visible.  Keys and values have the queries' head size.
+// causal; with a window, positions below `keep_first` stay visible.  Keys have the queries' head size, values `v_dim`
+// channels a head (64 or 128 each); out: [tokens, n_heads * v_dim].
 // Paged: k and v point into pools whose rows are `pool_row_stride` elements long (0: head_dim), so that one pool with
 // rows [key | value] serves both.
 extern "C" int bt_sigmoid_attention_tcgen05(const void* q, long long q_rows, long long q_row_stride, const void* k,
                                             const void* v, long long pool_pages, const int* kv_table, int table_stride,
                                             int table_len, int page_size, void* out, int* status, const int* seq_start,
                                             const int* past_len, int n_seqs, int max_new, int n_heads, int n_kv_heads,
-                                            int head_dim, float scale, const float* bias, int window, int keep_first,
-                                            long long pool_row_stride, cudaStream_t stream) {
+                                            int head_dim, int v_dim, float scale, const float* bias, int window,
+                                            int keep_first, long long pool_row_stride, cudaStream_t stream) {
   BT_CHECK(window >= 0 && keep_first >= 0, "sigmoid_attention_tcgen05: bad window %d or kept positions %d", window, keep_first);
   return run_attention_prefill_tcgen05(q, q_rows, q_row_stride, k, v, pool_pages, kv_table, table_stride, table_len, page_size,
                                        out, status, seq_start, past_len, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale,
-                                       1, window, 1, bias, keep_first, pool_row_stride, stream);
+                                       1, window, 1, bias, keep_first, pool_row_stride, v_dim, stream);
 }

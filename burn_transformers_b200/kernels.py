@@ -1440,43 +1440,46 @@ def sigmoid_attention_prep(proj, q_weight, k_weight, eps, positions, token_seq, 
 
 
 def sigmoid_attention_tcgen05_supports(dim: int, vdim: int, row_stride: int) -> bool:
-    """Whether sigmoid_attention_tcgen05 takes these sizes: keys and values of one size, 64 or 128 channels, rows of
+    """Whether sigmoid_attention_tcgen05 takes these sizes: keys and values of 64 or 128 channels a head each, rows of
     whole 16-byte pieces."""
-    return dim == vdim and row_stride % 8 == 0 and _supports("bt_attention_prefill_tcgen05_supports", dim, PAGE_SIZE)
+    return (row_stride % 8 == 0 and _supports("bt_attention_prefill_tcgen05_supports", dim, PAGE_SIZE)
+            and _supports("bt_attention_prefill_tcgen05_supports", vdim, PAGE_SIZE))
 
 
 def sigmoid_attention_tcgen05(proj, out, seq_start, past_len, *, n_seqs, max_new, n_heads, n_kv_heads, head_dim, scale,
-                              bias=None, window=0, keep_first=0, pool=None, table=None, table_len=0):
+                              v_dim=None, bias=None, window=0, keep_first=0, pool=None, table=None, table_len=0):
     """sigmoid_attention on the tcgen05 tensor cores (bfloat16; scores in tensor memory): `proj` rows hold the prepared
-    queries, keys and values one after another, heads of `head_dim` channels all three; out: [tokens, heads *
-    head_dim].  Keys and values are the step's own rows (sequences that start at position 0), or, with `pool`
-    [pages, kv_heads, PAGE_SIZE, 2 * head_dim] and `table`, the sequences' pages.  Scores and sigmoids in 32-bit; a
-    weight enters the value product rounded to bfloat16, the sums are 32-bit."""
-    _need(proj, "proj", torch.bfloat16, (None, (n_heads + 2 * n_kv_heads) * head_dim))
-    _need(out, "out", torch.bfloat16, (None, n_heads * head_dim))
+    queries, keys (heads of `head_dim` channels) and values (heads of `v_dim` channels, `head_dim` if not given) one
+    after another; out: [tokens, heads * v_dim].  Keys and values are the step's own rows (sequences that start at
+    position 0), or, with `pool` [pages, kv_heads, PAGE_SIZE, head_dim + v_dim] and `table`, the sequences' pages.
+    Scores and sigmoids in 32-bit; a weight enters the value product rounded to bfloat16, the sums are 32-bit."""
+    v_dim = head_dim if v_dim is None else v_dim
+    _need(proj, "proj", torch.bfloat16, (None, (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_dim))
+    _need(out, "out", torch.bfloat16, (None, n_heads * v_dim))
     if bias is not None:
         _need(bias, "bias", torch.float32, (n_heads,))
-    if not sigmoid_attention_tcgen05_supports(head_dim, head_dim, proj.shape[1]):
-        raise ShapeError(f"sigmoid_attention_tcgen05: heads of {head_dim} channels in rows of {proj.shape[1]}")
+    if not sigmoid_attention_tcgen05_supports(head_dim, v_dim, proj.shape[1]):
+        raise ShapeError(f"sigmoid_attention_tcgen05: heads of {head_dim} and {v_dim} channels in rows of {proj.shape[1]}")
     if _PROFILE is not None:
         ctx = float(_PROFILE.context_hint or 0)
         seen = min(ctx / 2, float(window + keep_first)) if window else ctx / 2
-        _work(4.0 * proj.shape[0] * n_heads * seen * head_dim, 2.0 * proj.shape[0] * (2 * n_heads + 2 * n_kv_heads) * head_dim)
-    q_width, kv_width = n_heads * head_dim, n_kv_heads * head_dim
+        _work(2.0 * proj.shape[0] * n_heads * seen * (head_dim + v_dim),
+              2.0 * proj.shape[0] * ((n_heads + n_kv_heads) * head_dim + (n_heads + n_kv_heads) * v_dim))
+    q_width, k_width = n_heads * head_dim, n_kv_heads * head_dim
     if table is None:
         k_ptr = c_void_p(proj.data_ptr() + q_width * 2)
-        v_ptr = c_void_p(proj.data_ptr() + (q_width + kv_width) * 2)
+        v_ptr = c_void_p(proj.data_ptr() + (q_width + k_width) * 2)
         t_ptr, t_stride, pages, row = c_void_p(0), 0, 0, 0
     else:
-        _need(pool, "pool", torch.bfloat16, (None, n_kv_heads, PAGE_SIZE, 2 * head_dim))
+        _need(pool, "pool", torch.bfloat16, (None, n_kv_heads, PAGE_SIZE, head_dim + v_dim))
         _need(table, "table", torch.int32)
         k_ptr, v_ptr = _ptr(pool), c_void_p(pool.data_ptr() + head_dim * 2)
-        t_ptr, t_stride, pages, row = _ptr(table), table.shape[1], pool.shape[0], 2 * head_dim
+        t_ptr, t_stride, pages, row = _ptr(table), table.shape[1], pool.shape[0], head_dim + v_dim
     _check(library().bt_sigmoid_attention_tcgen05(
         _ptr(proj), c_longlong(proj.shape[0]), c_longlong(proj.shape[1]), k_ptr, v_ptr, c_longlong(pages), t_ptr,
         c_int(t_stride), c_int(table_len), c_int(PAGE_SIZE), _ptr(out), _ptr(kernel_status(proj.device)), _ptr(seq_start),
-        _ptr(past_len), c_int(n_seqs), c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale),
-        _ptr(bias), c_int(window), c_int(keep_first), c_longlong(row), _stream()))
+        _ptr(past_len), c_int(n_seqs), c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(v_dim),
+        c_float(scale), _ptr(bias), c_int(window), c_int(keep_first), c_longlong(row), _stream()))
 
 
 def _grouped_views(q, k, v, out):

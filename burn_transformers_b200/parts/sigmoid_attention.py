@@ -37,7 +37,7 @@ class SigmoidAttention(Mixer):
 
     accepts_lazy_norm = False
     # Steps whose longest run of new tokens is at least this take a tensor-core kernel in bfloat16:
-    # csrc/attention_prefill_tcgen05.cu for keys and values of one size of 64 or 128 channels (fresh prompts over the
+    # csrc/attention_prefill_tcgen05.cu for keys and values of 64 or 128 channels a head each (fresh prompts over the
     # step's own rows, portions that continue a sequence over its pages), csrc/sink_attention_mma.cu for fresh prompts
     # of other sizes; everything else (decode steps, short portions, 32-bit, other sizes) takes the multiply-add kernels
     # over the pages.
@@ -121,13 +121,13 @@ class SigmoidAttention(Mixer):
         mixed = ctx.ws.take((n, self.n_heads * self.vdim), dtype)
         if dtype == torch.bfloat16 and not ctx.is_decode and ctx.max_new >= self.prompt_from:
             # prompts and their portions on tensor cores: tcgen05 with the scores in tensor memory where keys and values
-            # have one size the kernel is built for (fresh prompts attend over the step's own rows, portions that
-            # continue a sequence over its pages); else, for fresh prompts, `mma.sync`
+            # have sizes the kernel is built for (fresh prompts attend over the step's own rows, portions that continue
+            # a sequence over its pages); else, for fresh prompts, `mma.sync`
             if kernels.sigmoid_attention_tcgen05_supports(self.dim, self.vdim, self.proj_width):
                 paged = {} if ctx.fresh else {"pool": k_pool, "table": table, "table_len": group.table_len}
                 kernels.sigmoid_attention_tcgen05(proj, mixed, ctx.seq_start, ctx.past_len, n_seqs=ctx.n_seqs,
                                                   max_new=ctx.max_new, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
-                                                  head_dim=self.dim, scale=self.scale, bias=self.t_bias,
+                                                  head_dim=self.dim, v_dim=self.vdim, scale=self.scale, bias=self.t_bias,
                                                   window=self.window or 0, keep_first=self.keep_first, **paged)
                 linear(ctx, mixed, self.t_out_weight, self.t_out_bias, residual, m=n, residual=None if store else residual,
                        w_is_nk=True)

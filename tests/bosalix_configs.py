@@ -76,13 +76,14 @@ ODD = model(257, 72, 1e-6, 1.3, 1.0, [
 ])
 
 # C: larger heads (other branches of the kernels' size tables): 128 and 72 key channels a head, values of 96 and 130 channels, a
-# latent of 160 channels, sixteen query heads a key head; a layer whose keys and values have one size of 64 channels (the
-# tcgen05 kernel for fresh prompts).
+# latent of 160 channels, sixteen query heads a key head; two layers whose keys and values have 64 and 128 channels (the
+# tcgen05 kernel for prompts and their portions).
 LARGE = model(150, 80, 1e-5, 0.7, 4.0, [
     attention(16, 1, 128, 96, 0.09, 48, 1e6, window=70, keep_first=16, v_mix=True, mlp=moe(10, 3, 2, 88)),
     latent(6, 32, 16, 32, 160, 96, 0.14, 50000.0, window=50, mlp=moe(4, 4, 2, 64)),
     attention(4, 2, 72, 130, 0.12, 72, 10000.0, window=130, keep_first=1),
     attention(8, 2, 64, 64, 0.12, 32, 10000.0, window=90, keep_first=3, mlp=moe(3, 1, 2, 48)),
+    attention(4, 1, 64, 128, 0.12, 64, 10000.0, window=40, keep_first=40),
 ])
 
 # One mechanism at a time.

@@ -115,6 +115,8 @@ def sigmoid_case(rng, heads, groups, dim, vdim, rot_dims, news, pasts, dtype, mi
     (8, 2, 64, 64, 32, 100, 7, True),         # keys and values of one size the tcgen05 kernel takes; kept tiles before the window
     (4, 1, 128, 128, 128, 0, 0, False),       # the same at 128 channels, no window
     (6, 3, 64, 64, 64, 130, 129, False),      # kept positions that fill a tile of 128 and one more
+    (6, 2, 128, 64, 32, 90, 3, True),         # the tcgen05 kernel with values half as wide as the keys
+    (4, 4, 64, 128, 64, 200, 0, False),       # and twice as wide
 ])
 def test_sigmoid_attention_in_prompts_and_in_single_tokens(dtype, tol, heads, groups, dim, vdim, rot_dims, window, keep,
                                                            mixing):
@@ -160,8 +162,9 @@ def test_sigmoid_attention_in_prompts_and_in_single_tokens(dtype, tol, heads, gr
             # portions that continue a sequence (and single tokens) through the tcgen05 kernel over the pages
             fast = torch.full((n + 1, heads * vdim), 9.0, dtype=dtype, device=DEV)
             kernels.sigmoid_attention_tcgen05(rows, fast, seq_start, past, n_seqs=len(seqs), max_new=max(counts),
-                                              n_heads=heads, n_kv_heads=groups, head_dim=dim, scale=scale, bias=dev(bias),
-                                              window=window, keep_first=keep, pool=pool, table=pages, table_len=table_width)
+                                              n_heads=heads, n_kv_heads=groups, head_dim=dim, v_dim=vdim, scale=scale,
+                                              bias=dev(bias), window=window, keep_first=keep, pool=pool, table=pages,
+                                              table_len=table_width)
             kernels.check_status(torch.device(DEV))
             assert rel(host(fast[:n]), host(out[:n])) < tol and bool((fast[n:] == 9.0).all())
         if dtype == torch.bfloat16 and not any(pasts):
@@ -171,10 +174,10 @@ def test_sigmoid_attention_in_prompts_and_in_single_tokens(dtype, tol, heads, gr
             v = rows[:, (heads + groups) * dim:].view(n, groups, vdim)
             fast = torch.full((n + 1, heads, vdim), 9.0, dtype=dtype, device=DEV)
             if kernels.sigmoid_attention_tcgen05_supports(dim, vdim, rows.shape[1]):
-                # keys and values of one size of 64 or 128 channels: tcgen05, the scores in tensor memory
+                # keys and values of 64 or 128 channels a head each: tcgen05, the scores in tensor memory
                 kernels.sigmoid_attention_tcgen05(rows, fast.view(n + 1, -1), seq_start, past, n_seqs=len(seqs),
                                                   max_new=max(counts), n_heads=heads, n_kv_heads=groups, head_dim=dim,
-                                                  scale=scale, bias=dev(bias), window=window, keep_first=keep)
+                                                  v_dim=vdim, scale=scale, bias=dev(bias), window=window, keep_first=keep)
                 kernels.check_status(torch.device(DEV))
                 assert rel(host(fast[:n]).reshape(n, -1), host(out[:n])) < tol and bool((fast[n:] == 9.0).all())
                 fast.fill_(9.0)
